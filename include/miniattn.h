@@ -1,0 +1,98 @@
+/*
+ * miniattn.h — C ABI of the B200 (sm_100a) FlashAttention-2 forward operator.
+ *
+ * One shared library (libminiattn.so), plain pointers and sizes, no torch types.
+ * Every entry point returns 0 on success or a negative MINIATTN_E* code; the
+ * text of the last failure on the calling thread is returned by
+ * miniattn_last_error_string().  Nothing here throws, traps or blocks on the
+ * device: kernels are launched asynchronously on the caller's stream.
+ *
+ * Reference interfaces this replaces (paths inside ShlokVFX/Mini-Attention):
+ *   - ext.forward(kernel_cfg, q, k, v, o, benchmark) -> (Tensor, ms)
+ *       kernels/flash_attn/cuda/sm_120/kernel/flash_attention.cu:37-40,134-138
+ *   - ForwardKernelArgs (pointer + stride block handed to the device kernel)
+ *       kernels/flash_attn/cuda/sm_120/kernel/include/flash_attention.cuh:16-34
+ *   - forward(q, k, v) operator wrapper
+ *       kernels/flash_attn/cuda/sm86/inline/fp16_k1_sm86.py:265-269
+ */
+#ifndef MINIATTN_H_
+#define MINIATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MINIATTN_OK             0
+#define MINIATTN_EINVAL        -1   /* bad argument (null pointer, stride, size)          */
+#define MINIATTN_EUNSUPPORTED  -2   /* shape / dtype / device not supported               */
+#define MINIATTN_ECUDA         -3   /* CUDA runtime or driver call failed                 */
+#define MINIATTN_EDEVICE_WAIT  -4   /* a bounded device-side wait ran out (status word)   */
+
+#define MINIATTN_FP16 0
+#define MINIATTN_BF16 1
+
+/* kernel selector for MiniAttnFwdParams.kernel */
+#define MINIATTN_KERNEL_AUTO   0
+#define MINIATTN_KERNEL_SIMPLE 1    /* one 128-row Q tile per CTA, roles not specialised   */
+#define MINIATTN_KERNEL_WS     2    /* warp-specialised, two ping-ponged Q tiles per CTA   */
+
+/*
+ * Forward attention O = softmax(Q K^T * scale [+ causal mask]) V.
+ *
+ * Replaces ForwardKernelArgs + flash_attention_forward of the reference
+ * (flash_attention.cuh:16-34, flash_attention.cu:37-132) and widens it:
+ * per-tensor strides (so both the reference's (B,N,H,D) layout and (B,H,N,D)
+ * work without a copy), GQA/MQA head broadcast (Hkv divides Hq; KV head g
+ * serves query heads g*G .. g*G+G-1, as kernels/standard/pytorch/gqa.py:38-39),
+ * causal masking (key j visible to query i iff k_pos0+j <= q_pos0+i, as
+ * kernels/flash_attn/triton/fp16_flash_attn_sm86.py:55-58,74-75), optional
+ * log-sum-exp output.
+ *
+ * Strides are in ELEMENTS for the logical dims (batch, head, token); the head
+ * dim is contiguous (stride 1).  Every stride must be a multiple of 8 elements
+ * and every base pointer 16-byte aligned (TMA tensor-map rules).
+ */
+typedef struct MiniAttnFwdParams {
+  const void* q;          /* [B, Hq,  Nq, D] logical, device memory                */
+  const void* k;          /* [B, Hkv, Nk, D]                                       */
+  const void* v;          /* [B, Hkv, Nk, D]                                       */
+  void*       o;          /* [B, Hq,  Nq, D], same dtype as q                      */
+  float*      lse;        /* optional [B, Hq, Nq] fp32 contiguous: ln(sum exp)     */
+  int32_t*    status;     /* optional device word; kernels OR error bits into it   */
+  int64_t q_stride[3];    /* (batch, head, token) strides of q in elements         */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  int64_t q_pos0;         /* global position of q token 0 (causal test)            */
+  int64_t k_pos0;         /* global position of k token 0                          */
+  int32_t B, Hq, Hkv, Nq, Nk, D;
+  int32_t dtype;          /* MINIATTN_FP16 | MINIATTN_BF16                         */
+  int32_t causal;         /* 0 | 1                                                 */
+  float   softmax_scale;  /* <= 0 selects 1/sqrt(D) (the reference's fixed scale,  */
+                          /* forward_kernel.cuh:103-105)                           */
+  int32_t kernel;         /* MINIATTN_KERNEL_*                                     */
+} MiniAttnFwdParams;
+
+/* Launch the forward kernel on `stream` (a cudaStream_t; NULL = default stream). */
+int miniattn_fwd(const MiniAttnFwdParams* p, void* stream);
+
+/*
+ * Failure-detection self-test (no reference counterpart; the reference never checks
+ * its launches, flash_attention.cu:123).  Launches one CTA that waits on a barrier
+ * nothing signals.  The wait gives up after `limit_ns` nanoseconds (0 < limit_ns <= 2e9),
+ * ORs bit 30 into *status (device memory) and the kernel returns normally.
+ */
+int miniattn_selftest_wait(int32_t* status, uint64_t limit_ns, void* stream);
+
+/* Library / build identification: "miniattn-b200 <version> sm_100a". */
+const char* miniattn_version(void);
+
+/* Text of the last error recorded on the calling thread ("" if none). */
+const char* miniattn_last_error_string(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINIATTN_H_ */

@@ -1,0 +1,216 @@
+// Host side of the C ABI declared in include/miniattn.h: argument validation
+// (mirrors the checks of the reference launcher, kernels/flash_attn/cuda/sm_120/kernel/
+// flash_attention.cu:41-80, relaxed to "head dim contiguous" instead of fully contiguous),
+// TMA tensor-map construction from the caller's strides, kernel selection and launch.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/miniattn.h"
+#include "common.cuh"
+
+namespace ma {
+cudaError_t launch_fwd_simple(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
+                              cudaStream_t st);
+cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
+                          cudaStream_t st);
+cudaError_t launch_wait_selftest(int32_t* status, unsigned long long limit_ns, cudaStream_t st);
+}  // namespace ma
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 4-D map over a [B, H, N, D] logical tensor with arbitrary (batch, head, token) strides:
+// dims (fastest first) = (d, token, head, batch); box = 64 x `box_rows` x 1 x 1 elements
+// (one 128-byte swizzled row per token).
+int make_map(CUtensorMap* out, const void* base, int elem_bytes, CUtensorMapDataType dt, int D,
+             int N, int H, int B, const int64_t stride[3], int box_cols, int box_rows,
+             const char* what) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return fail(MINIATTN_ECUDA, "cuTensorMapEncodeTiled entry point not found");
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)stride[2] * elem_bytes, (cuuint64_t)stride[1] * elem_bytes,
+                           (cuuint64_t)stride[0] * elem_bytes};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  // a size-1 dim may carry any stride; give the encoder a legal one
+  for (int i = 0; i < 3; ++i)
+    if (dims[i + 1] == 1) strides[i] = (cuuint64_t)D * elem_bytes;
+  CUresult r = enc(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MINIATTN_ECUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  return MINIATTN_OK;
+}
+
+int check_tensor(const void* p, const int64_t s[3], int D, const char* name) {
+  if (p == nullptr) return fail(MINIATTN_EINVAL, "%s is null", name);
+  if (reinterpret_cast<uintptr_t>(p) % 16 != 0)
+    return fail(MINIATTN_EINVAL, "%s must be 16-byte aligned", name);
+  for (int i = 0; i < 3; ++i) {
+    if (s[i] < 0) return fail(MINIATTN_EINVAL, "%s has a negative stride", name);
+    if (s[i] % 8 != 0)
+      return fail(MINIATTN_EINVAL, "%s stride %d (%lld) is not a multiple of 8 elements", name, i,
+                  (long long)s[i]);
+  }
+  if (s[2] < D) return fail(MINIATTN_EINVAL, "%s token stride is smaller than D", name);
+  return MINIATTN_OK;
+}
+
+int device_sm_count(int* sms, int* major) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MINIATTN_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  static int cached_dev = -1, cached_sms = 0, cached_major = 0;
+  if (cached_dev != dev) {
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess)
+      return fail(MINIATTN_ECUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    cached_dev = dev;
+    cached_sms = prop.multiProcessorCount;
+    cached_major = prop.major;
+  }
+  *sms = cached_sms;
+  *major = cached_major;
+  return MINIATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* miniattn_version(void) { return "miniattn-b200 0.1 sm_100a"; }
+
+const char* miniattn_last_error_string(void) { return g_err; }
+
+int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
+  g_err[0] = 0;
+  if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
+  if (p->dtype != MINIATTN_FP16 && p->dtype != MINIATTN_BF16)
+    return fail(MINIATTN_EUNSUPPORTED, "dtype must be fp16 (0) or bf16 (1), got %d", p->dtype);
+  if (p->D != 64 && p->D != 128)
+    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64 or 128)", p->D);
+  if (p->B < 0 || p->Hq < 0 || p->Hkv < 0 || p->Nq < 0 || p->Nk < 0)
+    return fail(MINIATTN_EINVAL, "negative size");
+  if (p->B == 0 || p->Hq == 0 || p->Nq == 0) return MINIATTN_OK;  // empty output: nothing to do
+  if (p->Hkv == 0 || p->Hq % p->Hkv != 0)
+    return fail(MINIATTN_EINVAL, "Hq (%d) must be a positive multiple of Hkv (%d)", p->Hq, p->Hkv);
+  if (p->Hq > 65535 || p->B > 65535)
+    return fail(MINIATTN_EUNSUPPORTED, "B and Hq must not exceed 65535");
+  if (p->causal != 0 && p->causal != 1) return fail(MINIATTN_EINVAL, "causal must be 0 or 1");
+  if (p->kernel < MINIATTN_KERNEL_AUTO || p->kernel > MINIATTN_KERNEL_WS)
+    return fail(MINIATTN_EINVAL, "unknown kernel selector %d", p->kernel);
+  int rc;
+  if ((rc = check_tensor(p->q, p->q_stride, p->D, "q")) != 0) return rc;
+  if ((rc = check_tensor(p->o, p->o_stride, p->D, "o")) != 0) return rc;
+  // With no keys every row is fully masked; K/V pointers are still handed to the tensor-map
+  // encoder, so they must be valid whenever Nk > 0.
+  const bool has_keys = p->Nk > 0;
+  if (has_keys) {
+    if ((rc = check_tensor(p->k, p->k_stride, p->D, "k")) != 0) return rc;
+    if ((rc = check_tensor(p->v, p->v_stride, p->D, "v")) != 0) return rc;
+  }
+
+  int sms = 0, major = 0;
+  if ((rc = device_sm_count(&sms, &major)) != 0) return rc;
+  if (major != 10)
+    return fail(MINIATTN_EUNSUPPORTED,
+                "this library holds sm_100a code only; current device has compute capability %d.x",
+                major);
+
+  const CUtensorMapDataType dt =
+      p->dtype == MINIATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tm[4];
+  if ((rc = make_map(&tm[0], p->q, 2, dt, p->D, p->Nq, p->Hq, p->B, p->q_stride, ma::kBoxCols,
+                     ma::kTileM, "q")) != 0)
+    return rc;
+  if (has_keys) {
+    if ((rc = make_map(&tm[1], p->k, 2, dt, p->D, p->Nk, p->Hkv, p->B, p->k_stride, ma::kBoxCols,
+                       ma::kTileN, "k")) != 0)
+      return rc;
+    if ((rc = make_map(&tm[2], p->v, 2, dt, p->D, p->Nk, p->Hkv, p->B, p->v_stride, ma::kBoxCols,
+                       ma::kTileN, "v")) != 0)
+      return rc;
+  } else {
+    tm[1] = tm[0];
+    tm[2] = tm[0];
+  }
+  if ((rc = make_map(&tm[3], p->o, 2, dt, p->D, p->Nq, p->Hq, p->B, p->o_stride, ma::kBoxCols,
+                     ma::kTileM, "o")) != 0)
+    return rc;
+
+  ma::FwdArgs a;
+  a.lse = p->lse;
+  a.status = p->status;
+  a.q_pos0 = p->q_pos0;
+  a.k_pos0 = p->k_pos0;
+  a.Nq = p->Nq;
+  a.Nk = p->Nk;
+  a.Hq = p->Hq;
+  a.Hkv = p->Hkv;
+  a.B = p->B;
+  a.causal = p->causal;
+  a.scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)p->D);
+  a.scale_log2 = a.scale * 1.4426950408889634f;
+  a.n_q_tiles = (p->Nq + ma::kTileM - 1) / ma::kTileM;
+
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int kernel = p->kernel;
+  if (kernel == MINIATTN_KERNEL_AUTO) kernel = MINIATTN_KERNEL_WS;
+  cudaError_t e;
+  if (kernel == MINIATTN_KERNEL_SIMPLE)
+    e = ma::launch_fwd_simple(p->D, p->dtype == MINIATTN_BF16, tm, a, st);
+  else
+    e = ma::launch_fwd_ws(p->D, p->dtype == MINIATTN_BF16, tm, a, sms, st);
+  if (e != cudaSuccess)
+    return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return MINIATTN_OK;
+}
+
+int miniattn_selftest_wait(int32_t* status, uint64_t limit_ns, void* stream) {
+  g_err[0] = 0;
+  if (status == nullptr) return fail(MINIATTN_EINVAL, "status is null");
+  if (limit_ns == 0 || limit_ns > 2000000000ull)
+    return fail(MINIATTN_EINVAL, "limit_ns must be in (0, 2e9]");
+  cudaError_t e = ma::launch_wait_selftest(status, limit_ns, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess)
+    return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return MINIATTN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,11 @@
+"""miniattn — B200 (sm_100a) FlashAttention-2 forward operator behind the Python operator
+surface of ShlokVFX/Mini-Attention.  Importing the package loads libminiattn.so; there is no
+other backend and no CPU fallback."""
+from . import _lib
+from .ops import flash_attn_fwd, device_status, selftest_wait
+
+__all__ = ["flash_attn_fwd", "device_status", "selftest_wait", "version"]
+
+
+def version() -> str:
+    return _lib.lib.miniattn_version().decode()

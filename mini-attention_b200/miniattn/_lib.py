@@ -1,0 +1,62 @@
+"""ctypes binding of libminiattn.so (the C ABI in include/miniattn.h).
+
+There is no CPU fallback and no other backend: if the library is missing or fails to
+load, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "libminiattn.so"
+
+OK, EINVAL, EUNSUPPORTED, ECUDA, EDEVICE_WAIT = 0, -1, -2, -3, -4
+FP16, BF16 = 0, 1
+KERNEL_AUTO, KERNEL_SIMPLE, KERNEL_WS = 0, 1, 2
+KERNELS = {"auto": KERNEL_AUTO, "simple": KERNEL_SIMPLE, "ws": KERNEL_WS}
+
+
+class FwdParams(C.Structure):
+    """Mirror of ``MiniAttnFwdParams``."""
+
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
+        ("lse", C.c_void_p), ("status", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3),
+        ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
+        ("q_pos0", C.c_int64), ("k_pos0", C.c_int64),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32),
+        ("Nq", C.c_int32), ("Nk", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32),
+        ("softmax_scale", C.c_float), ("kernel", C.c_int32),
+    ]
+
+
+def _load() -> C.CDLL:
+    if not _LIB_PATH.exists():
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python mini-attention_b200/build.py` "
+            "(needs nvcc; there is no fallback path)"
+        )
+    lib = C.CDLL(str(_LIB_PATH))
+    lib.miniattn_fwd.argtypes = [C.POINTER(FwdParams), C.c_void_p]
+    lib.miniattn_fwd.restype = C.c_int
+    lib.miniattn_selftest_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.miniattn_selftest_wait.restype = C.c_int
+    lib.miniattn_version.restype = C.c_char_p
+    lib.miniattn_last_error_string.restype = C.c_char_p
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return lib.miniattn_last_error_string().decode()
+
+
+def check(rc: int, what: str) -> None:
+    """Turn a negative return code into the exception the reference raises (RuntimeError
+    from TORCH_CHECK, kernels/flash_attn/cuda/sm_120/kernel/flash_attention.cu:41-80)."""
+    if rc != OK:
+        raise RuntimeError(f"{what} failed ({rc}): {last_error()}")

@@ -1,0 +1,147 @@
+"""Python operator surface of the B200 forward-attention kernels.
+
+``flash_attn_fwd`` is the general entry ((B,H,N,D) or (B,N,H,D) tensors, causal,
+GQA/MQA head broadcast, optional log-sum-exp).  It validates like the reference launcher
+(kernels/flash_attn/cuda/sm_120/kernel/flash_attention.cu:41-80: CUDA tensors, equal
+fp16/bf16 dtypes, agreeing shapes) and raises ``RuntimeError`` on violation, launches on the
+current stream of the tensors' device and returns without synchronising.  torch is used for
+device memory and streams only; the arithmetic runs in libminiattn.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float16: _lib.FP16, torch.bfloat16: _lib.BF16}
+_status_words: dict = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index)
+    t = _status_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = t
+    return t
+
+
+def device_status(device: Union[torch.device, str, None] = None) -> int:
+    """Synchronise and return (then clear) the wait-timeout bits kernels raised on `device`."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    t = _status_word(device)
+    val = int(t.item())
+    if val:
+        t.zero_()
+    return val
+
+
+def _bhn_strides(t: torch.Tensor, layout: str) -> Tuple[int, int, int]:
+    if layout == "bhnd":
+        return t.stride(0), t.stride(1), t.stride(2)
+    return t.stride(0), t.stride(2), t.stride(1)
+
+
+def _bhnd_shape(t: torch.Tensor, layout: str) -> Tuple[int, int, int, int]:
+    if layout == "bhnd":
+        return tuple(t.shape)  # type: ignore[return-value]
+    b, n, h, d = t.shape
+    return b, h, n, d
+
+
+def flash_attn_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+    layout: str = "bhnd",
+    return_lse: bool = False,
+    out: Optional[torch.Tensor] = None,
+    kernel: str = "auto",
+    q_pos0: int = 0,
+    k_pos0: int = 0,
+):
+    """O = softmax(Q K^T * scale [+ causal mask]) V on the GPU.
+
+    q: (B,Hq,Nq,D) for ``layout="bhnd"`` or (B,Nq,Hq,D) for ``"bnhd"`` (the layout of the
+    reference CUDA operator, flash_attention.cu:68-70); k, v likewise with Hkv heads where
+    Hkv divides Hq (KV head g serves query heads g*G..g*G+G-1, as
+    kernels/standard/pytorch/gqa.py:38-39).  Causal: key j is visible to query i iff
+    ``k_pos0 + j <= q_pos0 + i`` (kernels/flash_attn/triton/fp16_flash_attn_sm86.py:74-75
+    with both offsets 0).  Returns ``out`` or ``(out, lse)`` with lse fp32 (B,Hq,Nq) =
+    natural-log of the softmax denominator.
+    """
+    if layout not in ("bhnd", "bnhd"):
+        raise RuntimeError(f"layout must be 'bhnd' or 'bnhd', got {layout!r}")
+    if kernel not in _lib.KERNELS:
+        raise RuntimeError(f"kernel must be one of {sorted(_lib.KERNELS)}, got {kernel!r}")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor")
+        if t.dim() != 4:
+            raise RuntimeError(f"{name} must be 4-D, got {t.dim()}-D")
+        if t.stride(-1) != 1 and t.numel() > 0:
+            raise RuntimeError(f"{name} must be contiguous in the head dimension")
+    if q.dtype not in _DTYPES:
+        raise RuntimeError("Only fp16 and bf16 are supported")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError("Input tensors must have the same data type")
+    if k.device != q.device or v.device != q.device:
+        raise RuntimeError("Input tensors must be on the same device")
+    B, Hq, Nq, D = _bhnd_shape(q, layout)
+    Bk, Hkv, Nk, Dk = _bhnd_shape(k, layout)
+    if _bhnd_shape(v, layout) != (Bk, Hkv, Nk, Dk):
+        raise RuntimeError("k and v must have the same shape")
+    if Bk != B or Dk != D:
+        raise RuntimeError("q and k/v must agree in batch size and head dim")
+    if Hkv == 0 or Hq % max(Hkv, 1) != 0:
+        raise RuntimeError(f"number of query heads ({Hq}) must be a multiple of KV heads ({Hkv})")
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        if out.shape != q.shape or out.dtype != q.dtype or out.device != q.device:
+            raise RuntimeError("out must match q in shape, dtype and device")
+        if out.stride(-1) != 1 and out.numel() > 0:
+            raise RuntimeError("out must be contiguous in the head dimension")
+    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device) if return_lse else None
+    if q.numel() == 0:
+        return (out, lse) if return_lse else out
+
+    p = _lib.FwdParams()
+    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.status = _status_word(q.device).data_ptr()
+    p.q_stride[:] = _bhn_strides(q, layout)
+    p.k_stride[:] = _bhn_strides(k, layout)
+    p.v_stride[:] = _bhn_strides(v, layout)
+    p.o_stride[:] = _bhn_strides(out, layout)
+    p.q_pos0, p.k_pos0 = int(q_pos0), int(k_pos0)
+    p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D = B, Hq, Hkv, Nq, Nk, D
+    p.dtype = _DTYPES[q.dtype]
+    p.causal = 1 if causal else 0
+    p.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
+    p.kernel = _lib.KERNELS[kernel]
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        rc = _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
+    _lib.check(rc, "miniattn_fwd")
+    return (out, lse) if return_lse else out
+
+
+def selftest_wait(limit_ms: float = 50.0, device: Union[torch.device, str, None] = None) -> int:
+    """Run the bounded-wait self-test kernel; returns the status word it produced."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = _lib.lib.miniattn_selftest_wait(C.c_void_p(status.data_ptr()), C.c_uint64(int(limit_ms * 1e6)),
+                                             C.c_void_p(stream))
+    _lib.check(rc, "miniattn_selftest_wait")
+    return int(status.item())
