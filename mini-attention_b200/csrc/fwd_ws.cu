@@ -1,8 +1,460 @@
+// Forward attention, warp-specialised sm_100a kernel.
+//
+// One CTA (512 threads) per work item = two 128-row Q tiles of one (batch, head).  The two
+// tiles are ping-ponged so that the exp2 / online-softmax work of one overlaps the
+// tensor-core work of the other.  Same math as the reference mainloop
+// (kernels/flash_attn/cuda/sm_120/kernel/include/forward_kernel.cuh:137-221 and
+// softmax.cuh:29-138), restructured for tcgen05 / TMEM / TMA:
+//
+//   warps 0-3   softmax of Q tile 0   (thread = one query row; S row read from TMEM)
+//   warps 4-7   softmax of Q tile 1
+//   warps 8-11  correction: rescales the O accumulators in TMEM when a row maximum moved,
+//               and runs the epilogue (O / l -> 16 bit -> swizzled smem -> TMA store)
+//   warp 12     MMA issuer: one thread issues every tcgen05.mma
+//   warp 13     TMA producer: Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring
+//   warps 14-15 idle (they donate their registers)
+//
+// TMEM (512 columns x 128 lanes x 32 bit): S0 [0,128)  S1 [128,256)  O0 [256,256+D)
+// O1 [256+D,256+2D).  P (16 bit) overwrites the first 64 columns of its S tile and is fed to
+// the PV MMA straight from TMEM (A operand), so P never touches shared memory.
+//
+// Tensor-pipe order per K/V tile j:  PV0(j)  S0(j+1)  PV1(j)  S1(j+1).
+//
+// The row maximum is updated lazily: a row keeps exponentiating against a stale maximum
+// until the true maximum has grown by more than 2^8 (in the exp2 domain), so the O
+// accumulator is rescaled only rarely; l is accumulated against the same maximum, which
+// keeps O / l exact.
 #include "common.cuh"
 #include "ptx.cuh"
+
 namespace ma {
-cudaError_t launch_fwd_simple(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, cudaStream_t st);
-cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count, cudaStream_t st) {
-  return launch_fwd_simple(D, bf16, tm, a, st);
+
+namespace {
+
+constexpr int kNumThreads = 512;
+// Register split per thread after setmaxnreg (8 softmax + 4 correction + 4 other warps;
+// 8*168 + 4*96 + 4*80 = 2048 = the 64 K registers of an SM divided by 32 lanes).
+#ifndef MA_REG_SOFTMAX
+#define MA_REG_SOFTMAX 168
+#define MA_REG_CORR 96
+#define MA_REG_OTHER 80
+#endif
+constexpr float kLazyThreshold = 8.0f;  // log2 units
+
+template <int D>
+struct WsLayout {
+  static constexpr int kBoxes = D / kBoxCols;
+  static constexpr int kTileBytes = kBoxes * kBoxBytes;  // Q, K or V tile (32 KB at D=128)
+  static constexpr int kStages = (D == 128) ? 4 : 8;     // ring slots, each one K or V tile
+  static constexpr int kOffQ = 0;                        // two Q tiles (reused as O staging)
+  static constexpr int kOffRing = 2 * kTileBytes;
+  static constexpr int kOffAlpha = kOffRing + kStages * kTileBytes;  // float[2][128]
+  static constexpr int kOffL = kOffAlpha + 1024;                     // float[2][128]
+  static constexpr int kOffBar = kOffL + 1024;
+  // barrier indices (8 bytes each)
+  static constexpr int kBarQFull = 0;                      // [2]
+  static constexpr int kBarKvFull = 2;                     // [kStages]
+  static constexpr int kBarKvEmpty = kBarKvFull + kStages; // [kStages]
+  static constexpr int kBarSFull = kBarKvEmpty + kStages;  // [2]  MMA -> softmax
+  static constexpr int kBarPReady = kBarSFull + 2;         // [2]  softmax -> MMA
+  static constexpr int kBarAlpha = kBarPReady + 2;         // [2]  softmax -> correction
+  static constexpr int kBarOReady = kBarAlpha + 2;         // [2]  correction -> MMA
+  static constexpr int kBarODone = kBarOReady + 2;         // [2]  MMA -> correction
+  static constexpr int kBarLReady = kBarODone + 2;         // [2]  softmax -> correction (final l)
+  static constexpr int kNumBars = kBarLReady + 2;
+  static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem slot, abort flag
+  static constexpr int kBytes = kOffMisc + 16;
+  static constexpr int kDynSmem = kBytes + 1024;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+__device__ __forceinline__ void warp_arrive(uint32_t bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
+}  // namespace
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kNumThreads, 1)
+fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+              const FwdArgs a) {
+  using L = WsLayout<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (sbase - raw);
+
+  const uint32_t sQ = sbase + L::kOffQ;
+  const uint32_t sRing = sbase + L::kOffRing;
+  float* alpha_smem = reinterpret_cast<float*>(gbase + L::kOffAlpha);
+  float* l_smem = reinterpret_cast<float*>(gbase + L::kOffL);
+  const uint32_t bars = sbase + L::kOffBar;
+  auto bar = [&](int idx) -> uint32_t { return bars + 8u * idx; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kOffMisc + 8);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- work item: heaviest (latest) Q tile pairs first; heads of one pair adjacent ----
+  const int n_pairs = (a.n_q_tiles + 1) >> 1;
+  const int bh_total = a.Hq * a.B;
+  const int item = blockIdx.x;
+  const int pair = n_pairs - 1 - item / bh_total;
+  const int bh = item % bh_total;
+  const int h = bh % a.Hq;
+  const int b = bh / a.Hq;
+  const int hk = h / (a.Hq / a.Hkv);
+  const int q0 = pair * 2 * kTileM;
+  const int nt = (q0 + kTileM < a.Nq) ? 2 : 1;  // Q tiles of this item that hold real rows
+
+  int kv_end = a.Nk;
+  if (a.causal) {
+    const int last_row = min(q0 + 2 * kTileM - 1, a.Nq - 1);
+    const long long vis = a.q_pos0 + last_row - a.k_pos0 + 1;
+    kv_end = static_cast<int>(max(0ll, min(static_cast<long long>(a.Nk), vis)));
+  }
+  const int n_tiles = (kv_end + kTileN - 1) / kTileN;
+
+  if (warp == 13 && lane == 0) {
+    mbar_init(bar(L::kBarQFull + 0), 1);
+    mbar_init(bar(L::kBarQFull + 1), 1);
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(bar(L::kBarKvFull + s), 1);
+      mbar_init(bar(L::kBarKvEmpty + s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar(L::kBarSFull + t), 1);
+      mbar_init(bar(L::kBarPReady + t), 4);
+      mbar_init(bar(L::kBarAlpha + t), 4);
+      mbar_init(bar(L::kBarOReady + t), 4);
+      mbar_init(bar(L::kBarODone + t), 1);
+      mbar_init(bar(L::kBarLReady + t), 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+    prefetch_tmap(&tm_o);
+  }
+  if (warp == 12) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx wc{abort_flag, a.status, MINIATTN_WAIT_LIMIT_NS};
+  const float c = a.scale_log2;
+
+  if (warp < 8) {
+    // =========================== softmax ===========================================
+    reg_inc<MA_REG_SOFTMAX>();
+    const int t = warp >> 2;
+    if (t < nt) {
+      const int r = tid & 127;
+      const int row = q0 + t * kTileM + r;
+      const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t tS = tmem_base + (t ? L::kColS1 : L::kColS0) + lane_off;
+      long long vis_ll = a.Nk;
+      if (a.causal) vis_ll = min(vis_ll, a.q_pos0 + row - a.k_pos0 + 1);
+      const int vis_row = static_cast<int>(max(0ll, vis_ll));
+      float m_cur = -INFINITY;
+      float l_run = 0.f;
+
+      for (int j = 0; j < n_tiles; ++j) {
+        mbar_wait(bar(L::kBarSFull + t), j & 1, wc, kErrWaitS);
+        tc_fence_after();
+        uint32_t s[4][32];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) tmem_ld32(tS + q * 32, s[q]);
+        tmem_wait_ld();
+
+        const int lim = vis_row - j * kTileN;
+        float mx = -INFINITY;
+        if (lim >= kTileN) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[q][i]));
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (q * 32 + i >= lim) s[q][i] = __float_as_uint(-INFINITY);
+              mx = fmaxf(mx, __uint_as_float(s[q][i]));
+            }
+        }
+        float alpha = 1.f;
+        if (j == 0) {
+          m_cur = mx;
+        } else {
+          const float m_new = fmaxf(m_cur, mx);
+          if ((m_new - m_cur) * c > kLazyThreshold) {  // also taken when m_cur = -inf
+            alpha = ex2((m_cur - m_new) * c);
+            m_cur = m_new;
+          }
+        }
+        alpha_smem[t * kTileM + r] = alpha;
+        warp_arrive(bar(L::kBarAlpha + t));
+
+        const float mc = (m_cur == -INFINITY) ? 0.f : m_cur * c;
+        float psum0 = 0.f, psum1 = 0.f;
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {  // 64 keys -> 32 packed columns per TMEM store
+          uint32_t pk[32];
+#pragma unroll
+          for (int qq = 0; qq < 2; ++qq) {
+            const int q = hb * 2 + qq;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = ex2(fmaf(__uint_as_float(s[q][i]), c, -mc));
+              const float p1 = ex2(fmaf(__uint_as_float(s[q][i + 1]), c, -mc));
+              psum0 += p0;
+              psum1 += p1;
+              pk[qq * 16 + (i >> 1)] = pack2<BF16>(p0, p1);
+            }
+          }
+          tmem_st32(tS + hb * 32, pk);
+        }
+        l_run = l_run * alpha + (psum0 + psum1);
+        tmem_wait_st();
+        tc_fence_before();
+        warp_arrive(bar(L::kBarPReady + t));
+      }
+
+      l_smem[t * kTileM + r] = l_run;
+      warp_arrive(bar(L::kBarLReady + t));
+      if (a.lse != nullptr && row < a.Nq) {
+        const float lse = (l_run > 0.f) ? (m_cur * a.scale + __logf(l_run)) : -INFINITY;
+        a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] = lse;
+      }
+    }
+  } else if (warp < 12) {
+    // =========================== correction + epilogue =============================
+    reg_dec<MA_REG_CORR>();
+    const int r = tid & 127;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    for (int j = 0; j < n_tiles; ++j) {
+      for (int t = 0; t < nt; ++t) {
+        mbar_wait(bar(L::kBarAlpha + t), j & 1, wc, kErrWaitCorr);
+        const float alpha = alpha_smem[t * kTileM + r];
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          mbar_wait(bar(L::kBarODone + t), (j - 1) & 1, wc, kErrWaitO);
+          tc_fence_after();
+          const uint32_t tO = tmem_base + (t ? L::kColO1 : L::kColO0) + lane_off;
+#pragma unroll
+          for (int q = 0; q < D / 32; ++q) {
+            uint32_t o[32];
+            tmem_ld32(tO + q * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + q * 32, o);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        }
+        warp_arrive(bar(L::kBarOReady + t));
+      }
+    }
+    // epilogue
+    for (int t = 0; t < nt; ++t) {
+      float inv_l = 0.f;
+      if (n_tiles > 0) {
+        mbar_wait(bar(L::kBarLReady + t), 0, wc, kErrWaitCorr);
+        const float l = l_smem[t * kTileM + r];
+        inv_l = (l > 0.f) ? (1.f / l) : 0.f;
+        mbar_wait(bar(L::kBarODone + t), (n_tiles - 1) & 1, wc, kErrWaitO);
+        tc_fence_after();
+      }
+      const uint32_t tO = tmem_base + (t ? L::kColO1 : L::kColO0) + lane_off;
+      const uint32_t stage = sQ + t * L::kTileBytes;
+#pragma unroll
+      for (int q = 0; q < D / 32; ++q) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tO + q * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int col = q * 32 + ch * 8;
+          const int bx = col >> 6;
+          const int chunk = (col & 63) >> 3;
+          const uint32_t addr = stage + bx * kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
+          const uint32_t w0 = pack2<BF16>(__uint_as_float(o[ch * 8 + 0]) * inv_l,
+                                          __uint_as_float(o[ch * 8 + 1]) * inv_l);
+          const uint32_t w1 = pack2<BF16>(__uint_as_float(o[ch * 8 + 2]) * inv_l,
+                                          __uint_as_float(o[ch * 8 + 3]) * inv_l);
+          const uint32_t w2 = pack2<BF16>(__uint_as_float(o[ch * 8 + 4]) * inv_l,
+                                          __uint_as_float(o[ch * 8 + 5]) * inv_l);
+          const uint32_t w3 = pack2<BF16>(__uint_as_float(o[ch * 8 + 6]) * inv_l,
+                                          __uint_as_float(o[ch * 8 + 7]) * inv_l);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
+                       "r"(w2), "r"(w3)
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(1, 128);
+      if (r == 0) {
+#pragma unroll
+        for (int bx = 0; bx < L::kBoxes; ++bx)
+          tma_store_4d(&tm_o, stage + bx * kBoxBytes, bx * kBoxCols, q0 + t * kTileM, h, b);
+        tma_store_commit();
+      }
+    }
+    if (r == 0) tma_store_wait_all();
+    tc_fence_before();
+  } else {
+    reg_dec<MA_REG_OTHER>();
+    if (warp == 12) {
+      // =========================== MMA issuer ======================================
+      if (lane == 0 && n_tiles > 0) {
+        constexpr uint32_t idesc_s = make_idesc(1, BF16 ? 1 : 0, 0, 0, kTileM, kTileN);
+        constexpr uint32_t idesc_o = make_idesc(1, BF16 ? 1 : 0, 0, 1, kTileM, D);
+        const uint32_t tS[2] = {tmem_base + L::kColS0, tmem_base + L::kColS1};
+        const uint32_t tO[2] = {tmem_base + L::kColO0, tmem_base + L::kColO1};
+        auto issue_s = [&](int t, int slot) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k / 4) * kBoxBytes + (k % 4) * 32;
+            const uint64_t da = make_smem_desc(sQ + t * L::kTileBytes + off, 16, 1024);
+            const uint64_t db = make_smem_desc(sRing + slot * L::kTileBytes + off, 16, 1024);
+            mma_f16_ss(tS[t], da, db, idesc_s, k > 0);
+          }
+        };
+        for (int t = 0; t < nt; ++t) mbar_wait(bar(L::kBarQFull + t), 0, wc, kErrWaitKV);
+        int cons = 0;  // ring consumption index: K_0, V_0, K_1, V_1, ...
+        mbar_wait(bar(L::kBarKvFull + 0), 0, wc, kErrWaitKV);
+        tc_fence_after();
+        for (int t = 0; t < nt; ++t) {
+          issue_s(t, 0);
+          mma_commit(bar(L::kBarSFull + t));
+        }
+        mma_commit(bar(L::kBarKvEmpty + 0));
+        cons = 1;
+        for (int j = 0; j < n_tiles; ++j) {
+          const int vslot = cons % L::kStages;
+          mbar_wait(bar(L::kBarKvFull + vslot), (cons / L::kStages) & 1, wc, kErrWaitKV);
+          ++cons;
+          const bool has_next = (j + 1 < n_tiles);
+          const int kslot = cons % L::kStages;
+          const uint32_t kpar = (cons / L::kStages) & 1;
+          for (int t = 0; t < nt; ++t) {
+            mbar_wait(bar(L::kBarPReady + t), j & 1, wc, kErrWaitP);
+            mbar_wait(bar(L::kBarOReady + t), j & 1, wc, kErrWaitCorr);
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < kTileN / 16; ++k) {
+              const uint64_t db =
+                  make_smem_desc(sRing + vslot * L::kTileBytes + k * 2048, kBoxBytes, 1024);
+              mma_f16_ts(tO[t], tS[t] + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+            }
+            mma_commit(bar(L::kBarODone + t));
+            if (t == nt - 1) mma_commit(bar(L::kBarKvEmpty + vslot));
+            if (has_next) {
+              if (t == 0) {
+                mbar_wait(bar(L::kBarKvFull + kslot), kpar, wc, kErrWaitKV);
+                tc_fence_after();
+              }
+              issue_s(t, kslot);
+              mma_commit(bar(L::kBarSFull + t));
+              if (t == nt - 1) mma_commit(bar(L::kBarKvEmpty + kslot));
+            }
+          }
+          if (has_next) ++cons;
+        }
+      }
+      __syncwarp();
+    } else if (warp == 13) {
+      // =========================== TMA producer ====================================
+      if (lane == 0 && n_tiles > 0) {
+        for (int t = 0; t < nt; ++t) {
+          mbar_expect_tx(bar(L::kBarQFull + t), L::kTileBytes);
+#pragma unroll
+          for (int bx = 0; bx < L::kBoxes; ++bx)
+            tma_load_4d(sQ + t * L::kTileBytes + bx * kBoxBytes, &tm_q, bar(L::kBarQFull + t),
+                        bx * kBoxCols, q0 + t * kTileM, h, b);
+        }
+        const int n_fill = 2 * n_tiles;
+        for (int i = 0; i < n_fill; ++i) {
+          const int slot = i % L::kStages;
+          const int use = i / L::kStages;
+          if (use > 0) mbar_wait(bar(L::kBarKvEmpty + slot), (use - 1) & 1, wc, kErrWaitFree);
+          const uint32_t fb = bar(L::kBarKvFull + slot);
+          mbar_expect_tx(fb, L::kTileBytes);
+          const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
+          const int j = i >> 1;
+#pragma unroll
+          for (int bx = 0; bx < L::kBoxes; ++bx)
+            tma_load_4d(sRing + slot * L::kTileBytes + bx * kBoxBytes, tm, fb, bx * kBoxCols,
+                        j * kTileN, hk, b);
+        }
+        // On the give-up path copies may still be in flight: let them land (bounded)
+        // before the CTA's shared memory is released.
+        if (*abort_flag) {
+          const uint64_t t0 = global_timer_ns();
+          while (global_timer_ns() - t0 < 2000000ull) {
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, L::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+template <int D, bool BF16>
+static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, cudaStream_t st) {
+  using L = WsLayout<D>;
+  auto kern = fwd_ws_kernel<D, BF16>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
+  if (e != cudaSuccess) return e;
+  const long long n_pairs = (a.n_q_tiles + 1) / 2;
+  const long long items = n_pairs * a.Hq * a.B;
+  if (items > 0x7fffffffll) return cudaErrorInvalidValue;
+  kern<<<static_cast<unsigned>(items), kNumThreads, L::kDynSmem, st>>>(tm[0], tm[1], tm[2], tm[3],
+                                                                       a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
+                          cudaStream_t st) {
+  (void)sm_count;
+  if (D == 128) return bf16 ? launch_ws_t<128, true>(tm, a, st) : launch_ws_t<128, false>(tm, a, st);
+  if (D == 64) return bf16 ? launch_ws_t<64, true>(tm, a, st) : launch_ws_t<64, false>(tm, a, st);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace ma
