@@ -1,0 +1,336 @@
+#!/usr/bin/env python
+"""Benchmark of the attention forward hot path.  Prints ONE JSON line.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workloads (``--workload``):
+  c2 (default)  MHA forward, non-causal, fp16, B=2 H=8 D=128 at N=8192 — the largest point of the
+                N = 512..8192 sweep the headline metric is quoted on; the other four N are timed
+                once each and reported under ``sweep``.  With --gpus N every rank runs its own
+                B=2 shard of a batch of 2*N (sharded by batch x head, no communication): weak scaling.
+  c3            GQA causal bf16 B=4 Hq=32 Hkv=8 N=4096 D=128, the (batch x KV-head) groups split
+                across the ranks, no communication: strong scaling.
+
+A step is one forward pass over one batch.  ``value`` is TFLOPS (4*B*H*N^2*D flops, halved for
+causal) with inputs resident in HBM, timed with CUDA events on the launch stream; L2 is flushed
+between steps (a 256 MiB write, outside the timed intervals).  ``e2e`` is the same metric through
+the public Python operator with pinned HOST buffers: host->device copies of q, k, v and the
+device->host copy of the output are inside the timed region.
+
+``--impl reference`` times the reference's CPU PyTorch attention path (restated in
+oracle/attention_oracle.py) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "mini-attention_b200"))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    "c2": dict(B=2, Hq=8, Hkv=8, N=8192, D=128, dtype="fp16", causal=False,
+               name="MHA fwd non-causal fp16 B=2 H=8 N=8192 D=128 (top of the N=512..8192 sweep)"),
+    "c3": dict(B=4, Hq=32, Hkv=8, N=4096, D=128, dtype="bf16", causal=True,
+               name="GQA fwd causal bf16 B=4 Hq=32 Hkv=8 N=4096 D=128, (batch x KV-head) groups sharded"),
+}
+SWEEP_N = (512, 1024, 2048, 4096)
+METRIC = "attention fwd TFLOPS (fp16, D=128, N=512-8192) and % of B200 dense peak"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of fwd_ws_kernel from the ncu capture
+# summarised under profiles/ (workload key -> bytes); None until a capture exists.
+NCU_TRAFFIC_BYTES = {}
+
+
+def flops(B, H, N, D, causal):
+    f = 4.0 * B * H * N * N * D
+    return f / 2 if causal else f
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["bf16_tflops"]), "measured burst (MEASURED_PEAKS.json bf16_tflops)"
+        except Exception:
+            pass
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------- CPU arm
+def cpu_attention_sample(w, budget_s: float):
+    """Time the reference's CPU PyTorch attention on (batch, head) slices of the workload until
+    about `budget_s` seconds are spent.  Returns (TFLOPS, cores, description)."""
+    import torch.nn.functional as F
+    from oracle.attention_oracle import attention_reference, make_inputs
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    dt = torch.float16 if w["dtype"] == "fp16" else torch.bfloat16
+    G = w["Hq"] // w["Hkv"]
+    # one KV-head group (G query heads sharing one KV head) of one batch element per unit
+    q, k, v = make_inputs(1, G, 1, w["N"], w["N"], w["D"], dt, seed=0)
+    unit_flops = flops(1, G, w["N"], w["D"], w["causal"])
+    total_units = w["B"] * w["Hkv"]
+
+    def sdpa():  # the reference test's call (tests/test_correctness.py:35-43), GQA by expand
+        return F.scaled_dot_product_attention(q, k.expand(-1, G, -1, -1), v.expand(-1, G, -1, -1),
+                                              is_causal=w["causal"])
+
+    def explicit():  # reference() of the Triton file: fp32 matmul / softmax / matmul
+        return attention_reference(q, k, v, causal=w["causal"])
+
+    best = None
+    for name, fn in (("F.scaled_dot_product_attention", sdpa), ("fp32 matmul-softmax-matmul", explicit)):
+        t0 = time.perf_counter()
+        fn()
+        first = time.perf_counter() - t0
+        reps = max(1, min(total_units, int((budget_s / 2) / max(first, 1e-3))))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        dt_s = (time.perf_counter() - t0) / reps
+        tf = unit_flops / dt_s / 1e12
+        if best is None or tf > best[0]:
+            best = (tf, name, reps)
+    tf, name, reps = best
+    desc = (f"{name} on CPU, {reps} of {total_units} (batch x KV-head) units of the workload "
+            f"(each {G} query head(s) x N={w['N']}), {cores} threads")
+    return tf, cores, desc
+
+
+def run_reference_arm(args, w, rank):
+    if rank != 0:
+        return
+    vals = []
+    desc = ""
+    cores = os.cpu_count() or 1
+    t_begin = time.perf_counter()
+    for _ in range(args.warmup):
+        cpu_attention_sample(w, 1.0)
+    for _ in range(args.steps):
+        tf, cores, desc = cpu_attention_sample(w, max(2.0, 60.0 / max(args.steps, 1)))
+        vals.append(tf)
+    value = statistics.mean(vals)
+    step_units = 1
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": (time.perf_counter() - t_begin) * 1e3 / max(args.steps + args.warmup, 1),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w["dtype"], "data": "synthetic", "config": {"workload": w["name"]},
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--kernel", default="auto")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, rank)
+        return
+
+    args.warmup = max(args.warmup, 3)
+    import miniattn
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dt = torch.float16 if w["dtype"] == "fp16" else torch.bfloat16
+    B, Hq, Hkv, N, D, causal = w["B"], w["Hq"], w["Hkv"], w["N"], w["D"], w["causal"]
+    if args.workload == "c3":
+        # strong scaling: split the B*Hkv groups (whole groups stay on one GPU); per-rank tensors
+        # are (1, G*groups, N, D) / (1, groups, N, D)
+        groups = B * Hkv
+        assert groups % world == 0, "group count must divide by the number of GPUs"
+        per = groups // world
+        G = Hq // Hkv
+        shard = dict(B=1, Hq=per * G, Hkv=per)
+        scaling = "strong"
+        total_flops = flops(B, Hq, N, D, causal)
+    else:
+        shard = dict(B=B, Hq=Hq, Hkv=Hkv)
+        scaling = "weak"
+        total_flops = flops(B, Hq, N, D, causal) * world
+    sB, sHq, sHkv = shard["B"], shard["Hq"], shard["Hkv"]
+    step_flops = flops(sB, sHq, N, D, causal)
+
+    g = torch.Generator().manual_seed(1234 + rank)
+    hq = torch.randn(sB, sHq, N, D, generator=g).to(dt).pin_memory()
+    hk = torch.randn(sB, sHkv, N, D, generator=g).to(dt).pin_memory()
+    hv = torch.randn(sB, sHkv, N, D, generator=g).to(dt).pin_memory()
+    ho = torch.empty_like(hq).pin_memory()
+    q, k, v = hq.to(dev), hk.to(dev), hv.to(dev)
+    o = torch.empty_like(q)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def step_device():
+        miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel)
+
+    def step_e2e():
+        q.copy_(hq, non_blocking=True)
+        k.copy_(hk, non_blocking=True)
+        v.copy_(hv, non_blocking=True)
+        miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel)
+        ho.copy_(o, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            flush.zero_()
+            fn()
+        barrier()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for a, b_ in evs:
+            flush.zero_()
+            a.record(stream)
+            fn()
+            b_.record(stream)
+        barrier()
+        ms = sum(a.elapsed_time(b_) for a, b_ in evs)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms_dev = timed(step_device, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3)
+    status = miniattn.device_status(dev)
+
+    sweep = {}
+    if args.workload == "c2" and rank == 0:
+        for n in SWEEP_N:
+            qs = torch.randn(B, Hq, n, D, device=dev, dtype=dt)
+            ks, vs = torch.randn_like(qs), torch.randn_like(qs)
+            os_ = torch.empty_like(qs)
+            fn = lambda: miniattn.flash_attn_fwd(qs, ks, vs, out=os_, kernel=args.kernel)  # noqa: E731
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(dev)
+            tot = 0.0
+            for _ in range(10):
+                flush.zero_()
+                a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream); fn(); b_.record(stream)
+                b_.synchronize()
+                tot += a.elapsed_time(b_)
+            sweep[str(n)] = {"ms": tot / 10, "tflops": flops(B, Hq, n, D, False) / (tot / 10) / 1e9}
+    if world > 1:
+        dist.barrier()
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        value = total_flops / ms_dev / 1e9
+        achieved = step_flops / ms_dev / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["name"], "per_gpu": shard, "seq_len": N, "head_dim": D, "causal": causal,
+                       "parallelism": f"batch x head shards over {world} GPU(s), no communication",
+                       "l2": "flushed between steps (256 MiB write outside the timed intervals)",
+                       "timing": "sum of per-step CUDA-event intervals on the launch stream, max over ranks"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                         "peak_source": peak_src, "frac_of_nominal_2250": achieved / 2250.0,
+                         "algorithmic_flops_per_launch": step_flops,
+                         "algorithmic_hbm_bytes_per_launch": (2 * sHq + 2 * sHkv) * sB * N * D * 2,
+                         "hbm_gbs": (2 * sHq + 2 * sHkv) * sB * N * D * 2 / ms_dev / 1e6},
+            "e2e": {"value": total_flops / ms_e2e / 1e9, "unit": "TFLOPS", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": hq.numel() * 2 + hk.numel() * 2 + hv.numel() * 2,
+                    "d2h_bytes_per_step": ho.numel() * 2},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+            "device_status": status,
+            "kernel": args.kernel,
+        }
+        if sweep:
+            line["sweep"] = sweep
+        if world == 1 and not args.no_cpu_baseline:
+            tf, cores, desc = cpu_attention_sample(w, 20.0)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

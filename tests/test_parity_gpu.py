@@ -1,0 +1,245 @@
+"""Parity of the CUDA path (called through the C ABI via miniattn) with the CPU oracle, the
+golden fixtures produced by the reference's own PyTorch code, and size-independent properties
+at the full BASELINE sizes.
+
+Tolerances (max |out - reference|): fp16 2e-3, bf16 1e-2 — the north-star bars; they are
+spelled out in conftest.TOL.
+"""
+import math
+
+import pytest
+import torch
+
+import miniattn
+from conftest import TOL, golden_names, load_golden
+from oracle.attention_oracle import (attention_reference, attention_reference_rows, make_inputs,
+                                     sdpa_reference_bnhd)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+KERNELS = ["ws", "simple"]
+
+
+def run(q, k, v, **kw):
+    out = miniattn.flash_attn_fwd(q.to(DEV), k.to(DEV), v.to(DEV), **kw)
+    if isinstance(out, tuple):
+        res = tuple(o.cpu() for o in out)
+    else:
+        res = out.cpu()
+    assert miniattn.device_status(DEV) == 0, "a bounded device wait ran out"
+    return res
+
+
+def maxerr(a, b):
+    return (a.float() - b.float()).abs().max().item()
+
+
+# ------------------------------------------------------------------ small-case sweep
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize(
+    "B,Hq,Hkv,Nq,Nk,D",
+    [
+        (1, 1, 1, 128, 128, 128),
+        (1, 2, 2, 256, 256, 64),
+        (2, 4, 1, 384, 384, 128),   # MQA
+        (1, 8, 2, 512, 512, 128),   # GQA, 4 query heads per KV head
+        (1, 2, 2, 200, 333, 128),   # ragged: neither length is a multiple of the tile
+        (1, 3, 3, 1, 77, 64),       # a single query row
+        (1, 2, 1, 640, 96, 64),     # more queries than keys
+        (2, 2, 2, 129, 1, 128),     # a single key
+    ],
+)
+def test_small_cases(kernel, dtype, causal, B, Hq, Hkv, Nq, Nk, D):
+    q, k, v = make_inputs(B, Hq, Hkv, Nq, Nk, D, dtype, seed=Nq * 7 + Nk)
+    ref, ref_lse = attention_reference(q, k, v, causal=causal, return_lse=True, out_dtype=torch.float32)
+    out, lse = run(q, k, v, causal=causal, kernel=kernel, return_lse=True)
+    assert out.dtype == dtype
+    assert maxerr(out, ref) <= TOL[dtype]
+    finite = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), finite)
+    assert (lse[finite] - ref_lse[finite]).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_softmax_scale_and_layouts(kernel):
+    q, k, v = make_inputs(2, 4, 4, 256, 256, 128, torch.float16, seed=11)
+    ref = attention_reference(q, k, v, softmax_scale=0.05, out_dtype=torch.float32)
+    assert maxerr(run(q, k, v, softmax_scale=0.05, kernel=kernel), ref) <= TOL[torch.float16]
+    # (B,N,H,D) tensors, as the reference CUDA operator takes them
+    qn, kn, vn = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    out = run(qn, kn, vn, softmax_scale=0.05, layout="bnhd", kernel=kernel)
+    assert maxerr(out.transpose(1, 2), ref) <= TOL[torch.float16]
+    # strided views: every other head of a wider tensor, no copy
+    wide = torch.randn(2, 8, 256, 128, dtype=torch.float16)
+    qs = wide[:, ::2]
+    ref2 = attention_reference(qs, k, v, out_dtype=torch.float32)
+    out2 = miniattn.flash_attn_fwd(wide.to(DEV)[:, ::2], k.to(DEV), v.to(DEV), kernel=kernel).cpu()
+    assert maxerr(out2, ref2) <= TOL[torch.float16]
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_causal_offsets(kernel):
+    """Global positions shift the diagonal (what a ring step needs); rows that see no key give
+    zeros and lse = -inf."""
+    q, k, v = make_inputs(1, 2, 2, 256, 384, 128, torch.float16, seed=5)
+    for q_pos0, k_pos0 in ((128, 0), (0, 128), (300, 100), (0, 400)):
+        ref, ref_lse = attention_reference(q, k, v, causal=True, q_pos0=q_pos0, k_pos0=k_pos0,
+                                           return_lse=True, out_dtype=torch.float32)
+        out, lse = run(q, k, v, causal=True, q_pos0=q_pos0, k_pos0=k_pos0, kernel=kernel, return_lse=True)
+        assert maxerr(out, ref) <= TOL[torch.float16], (q_pos0, k_pos0)
+        finite = torch.isfinite(ref_lse)
+        assert torch.equal(torch.isfinite(lse), finite)
+        if finite.any():
+            assert (lse[finite] - ref_lse[finite]).abs().max().item() <= 2e-3
+
+
+# ------------------------------------------------------------------ golden fixtures
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name", [n for n in golden_names() if n.startswith("triton_reference")])
+def test_golden_triton_reference(kernel, name):
+    g = load_golden(name)
+    out = run(g["q"], g["k"], g["v"], causal=bool(g["causal"]), kernel=kernel)
+    assert maxerr(out, g["out"]) <= TOL[g["q"].dtype]
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name", ["gqa_core", "mqa_core", "mha_core_full", "mha_core_masked"])
+def test_golden_standard_modules(kernel, name):
+    """Core attention call of GQA_Flash / MQA_Flash / MHA: fp32 fixtures, run here in fp16."""
+    g = load_golden(name)
+    out = run(g["q"].half(), g["k"].half(), g["v"].half(), causal=bool(g["causal"]), kernel=kernel)
+    assert maxerr(out, g["out"]) <= 3e-3  # fp16 tolerance + rounding of the fp32 inputs to fp16
+
+
+def test_golden_reference_test_recipe():
+    """The reference's tests/test_correctness.py through the compat operator: seed 42,
+    (B,N,H,D) = (2,512,8,128) fp16, its own tolerance 1e-3."""
+    g = load_golden("sdpa_bnhd_test_correctness")
+    torch.manual_seed(int(g["seed"]))
+    q = torch.randn(int(g["B"]), int(g["N"]), int(g["H"]), int(g["D"]), dtype=torch.float16)
+    k = torch.randn_like(q)
+    v = torch.randn_like(q)
+    out = miniattn.forward(q.to(DEV), k.to(DEV), v.to(DEV)).cpu()
+    assert maxerr(out[:, :: int(g["row_step"])], g["out_rows"]) < float(g["tolerance"])
+    cfg = miniattn.kernel_configs.get_kernel_progression_configs()[6]
+    o2, ms = miniattn.ext.forward(cfg, q.to(DEV), k.to(DEV), v.to(DEV), None, True)
+    assert ms > 0 and torch.equal(o2.cpu(), out)
+    g2 = load_golden("sdpa_bnhd_small")
+    assert maxerr(miniattn.forward(g2["q"].to(DEV), g2["k"].to(DEV), g2["v"].to(DEV)).cpu(), g2["out"]) < 1e-3
+
+
+def test_compat_error_behaviour():
+    q = torch.zeros(1, 96, 2, 128, dtype=torch.float16, device=DEV)
+    cfg = miniattn.kernel_configs.get_kernel_progression_configs()[0]
+    with pytest.raises(RuntimeError, match="multiple of the block sizes"):
+        miniattn.ext.forward(cfg, q, q, q, None, False)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        miniattn.ext.forward(cfg, q.transpose(1, 2), q, q, None, False)
+    with pytest.raises(RuntimeError, match="dtype"):
+        miniattn.ext.forward(cfg, q.bfloat16(), q.bfloat16(), q.bfloat16(), None, False)
+    with pytest.raises(RuntimeError, match="same data type"):
+        miniattn.ext.forward(None, q, q.bfloat16(), q, None, False)
+
+
+# ------------------------------------------------------------------ BASELINE configurations
+def test_config1_full_oracle():
+    """MHA fp16 B=2 H=8 N=512 D=128, seed 0, (B,H,N,D)."""
+    q, k, v = make_inputs(2, 8, 8, 512, 512, 128, torch.float16, seed=0)
+    ref = attention_reference(q, k, v, out_dtype=torch.float32)
+    for kernel in KERNELS:
+        assert maxerr(run(q, k, v, kernel=kernel), ref) <= TOL[torch.float16]
+
+
+@pytest.mark.parametrize("N", [1024, 2048, 4096, 8192])
+def test_config2_sweep(N):
+    """Config 2 at every N: sampled rows against the exact oracle, plus the two kernels agree."""
+    q, k, v = make_inputs(2, 8, 8, N, N, 128, torch.float16, seed=0)
+    rows = torch.cat([torch.tensor([0, 1, 127, 128, N // 2, N - 129, N - 128, N - 1]),
+                      torch.randint(0, N, (120,), generator=torch.Generator().manual_seed(N))]).unique()
+    ref_rows = attention_reference_rows(q, k, v, rows)
+    out = run(q, k, v, kernel="ws")
+    assert maxerr(out[:, :, rows], ref_rows) <= TOL[torch.float16]
+    out_s = run(q, k, v, kernel="simple")
+    assert maxerr(out, out_s) <= TOL[torch.float16]
+
+
+def test_config3_gqa_causal_bf16():
+    """GQA causal bf16 B=4 Hq=32 Hkv=8 N=4096 D=128: sampled rows vs the oracle."""
+    q, k, v = make_inputs(4, 32, 8, 4096, 4096, 128, torch.bfloat16, seed=0)
+    rows = torch.cat([torch.tensor([0, 1, 127, 128, 255, 256, 2047, 4095]),
+                      torch.randint(0, 4096, (56,), generator=torch.Generator().manual_seed(3))]).unique()
+    ref_rows = attention_reference_rows(q, k, v, rows, causal=True)
+    out = run(q, k, v, causal=True)
+    assert maxerr(out[:, :, rows], ref_rows) <= TOL[torch.bfloat16]
+
+
+# ------------------------------------------------------------------ properties at full size
+@pytest.mark.parametrize("causal", [False, True])
+def test_properties_full_size(causal):
+    N, D = 8192, 128
+    q, k, v = make_inputs(1, 4, 4, N, N, D, torch.float16, seed=9)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    # V constant per channel -> every output row equals that constant
+    const = torch.linspace(-2, 2, D, dtype=torch.float16, device=DEV).expand(1, 4, N, D).contiguous()
+    out = miniattn.flash_attn_fwd(qd, kd, const, causal=causal)
+    assert maxerr(out, const) <= 2e-3
+    # K = 0 -> uniform weights: O = mean of the visible V rows (prefix mean when causal)
+    out = miniattn.flash_attn_fwd(qd, torch.zeros_like(kd), vd, causal=causal).float()
+    if causal:
+        expect = vd.float().cumsum(dim=2) / torch.arange(1, N + 1, device=DEV).view(1, 1, N, 1)
+    else:
+        expect = vd.float().mean(dim=2, keepdim=True).expand_as(out)
+    assert maxerr(out, expect) <= 2e-3
+    # linearity in V: O(V1 + V2) = O(V1) + O(V2)
+    v2 = torch.randn_like(vd)
+    o1 = miniattn.flash_attn_fwd(qd, kd, vd, causal=causal).float()
+    o2 = miniattn.flash_attn_fwd(qd, kd, v2, causal=causal).float()
+    o12 = miniattn.flash_attn_fwd(qd, kd, (vd.float() + v2.float()).half(), causal=causal).float()
+    assert maxerr(o12, o1 + o2) <= 6e-3
+    if not causal:
+        # permuting the keys (with their values) leaves the result unchanged
+        perm = torch.randperm(N, device=DEV)
+        o_perm = miniattn.flash_attn_fwd(qd, kd[:, :, perm].contiguous(), vd[:, :, perm].contiguous()).float()
+        assert maxerr(o_perm, o1) <= 2e-3
+    # a huge logit on one key -> the output is that key's value row
+    kk = kd.clone()
+    qq = qd.clone()
+    qq[:, :, :, 0] = 40.0
+    kk[:, :, :, 0] = 0.0
+    kk[:, :, 5, 0] = 40.0
+    o_hot = miniattn.flash_attn_fwd(qq, kk, vd, causal=causal, softmax_scale=1.0).float()
+    assert maxerr(o_hot[:, :, 5:], vd[:, :, 5:6].float().expand(-1, -1, N - 5, -1)) <= 2e-3
+    assert miniattn.device_status(DEV) == 0
+
+
+def test_bounded_wait_self_test():
+    """A device-side wait that nothing satisfies gives up, reports bit 30 and leaves the context usable."""
+    assert miniattn.selftest_wait(20.0) == (1 << 30)
+    q, k, v = make_inputs(1, 1, 1, 128, 128, 128, torch.float16, seed=1)
+    assert maxerr(run(q, k, v), attention_reference(q, k, v, out_dtype=torch.float32)) <= 2e-3
+
+
+def test_variant_modules_match_reference_math():
+    """MHA / GQA_Flash / MQA_Flash modules vs the same module math done with the oracle."""
+    torch.manual_seed(0)
+    x = torch.randn(2, 256, 512).half()
+    for mod, hq, hkv in ((miniattn.GQA_Flash(512, 8, 2), 8, 2), (miniattn.MQA_Flash(512, 4), 4, 1)):
+        mod = mod.half()
+        y = mod.to(DEV)(x.to(DEV)).float().cpu()
+        mod = mod.cpu().float()
+        xf = x.float()
+        dh = 512 // hq
+        q = mod.w_q(xf).view(2, 256, hq, dh).transpose(1, 2)
+        kvp = (mod.kv if hasattr(mod, "kv") else mod.k_v)(xf).view(2, 256, 2, hkv, dh)
+        kk, vv = kvp[:, :, 0].transpose(1, 2), kvp[:, :, 1].transpose(1, 2)
+        o = attention_reference(q.half(), kk.half(), vv.half(), causal=True, out_dtype=torch.float32)
+        y_ref = mod.w_o(o.transpose(1, 2).reshape(2, 256, 512))
+        assert maxerr(y, y_ref.detach()) <= 2e-2
+    mha = miniattn.MHA(512, 4).half().to(DEV)
+    y0 = mha(x.to(DEV))
+    y1 = mha(x.to(DEV), mask=torch.tril(torch.ones(256, 256, device=DEV)))
+    assert y0.shape == y1.shape == (2, 256, 512) and not torch.equal(y0, y1)
+    with pytest.raises(RuntimeError, match="lower-triangular"):
+        mha(x.to(DEV), mask=torch.ones(256, 256, device=DEV))
