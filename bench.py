@@ -180,12 +180,14 @@ def run_reference_arm(args, w, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--kernel", default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the one-shot timings of the smaller N")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     rank = int(os.environ.get("RANK", "0"))
@@ -270,13 +272,15 @@ def main():
         return ms / steps
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler is not None:
+        time.sleep(0.6)  # let nvidia-smi start sampling before the timed region
     ms_dev = timed(step_device, args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
-    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3)
+    ms_e2e = ms_dev if args.no_e2e else timed(step_e2e, max(3, args.steps // 2), 3)
     status = miniattn.device_status(dev)
 
     sweep = {}
-    if args.workload == "c2" and rank == 0:
+    if args.workload == "c2" and rank == 0 and not args.no_sweep:
         for n in SWEEP_N:
             qs = torch.randn(B, Hq, n, D, device=dev, dtype=dt)
             ks, vs = torch.randn_like(qs), torch.randn_like(qs)
@@ -314,9 +318,10 @@ def main():
                          "algorithmic_flops_per_launch": step_flops,
                          "algorithmic_hbm_bytes_per_launch": (2 * sHq + 2 * sHkv) * sB * N * D * 2,
                          "hbm_gbs": (2 * sHq + 2 * sHkv) * sB * N * D * 2 / ms_dev / 1e6},
-            "e2e": {"value": total_flops / ms_e2e / 1e9, "unit": "TFLOPS", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": hq.numel() * 2 + hk.numel() * 2 + hv.numel() * 2,
-                    "d2h_bytes_per_step": ho.numel() * 2},
+            "e2e": None if args.no_e2e else {
+                "value": total_flops / ms_e2e / 1e9, "unit": "TFLOPS", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": hq.numel() * 2 + hk.numel() * 2 + hv.numel() * 2,
+                "d2h_bytes_per_step": ho.numel() * 2},
             "gpu_launches": args.steps,
             "clocks": clocks,
             "device_status": status,
