@@ -25,6 +25,9 @@ cudaError_t launch_wait_selftest(int32_t* status, unsigned long long limit_ns, c
 namespace {
 
 thread_local char g_err[512] = "";
+#ifdef MA_TRACE
+unsigned long long* g_trace = nullptr;
+#endif
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -188,6 +191,10 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
   a.scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)p->D);
   a.scale_log2 = a.scale * 1.4426950408889634f;
   a.n_q_tiles = (p->Nq + ma::kTileM - 1) / ma::kTileM;
+  a.trace = nullptr;
+#ifdef MA_TRACE
+  a.trace = g_trace;
+#endif
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int kernel = p->kernel;
@@ -201,6 +208,10 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;
 }
+
+#ifdef MA_TRACE
+void miniattn_debug_set_trace(unsigned long long* p) { g_trace = p; }
+#endif
 
 int miniattn_selftest_wait(int32_t* status, uint64_t limit_ns, void* stream) {
   g_err[0] = 0;

@@ -15,6 +15,7 @@ struct FwdArgs {
   float scale;         // softmax scale
   float scale_log2;    // softmax scale * log2(e)
   int n_q_tiles;       // ceil(Nq / 128)
+  unsigned long long* trace;  // debug builds only (MA_TRACE): per-role clock stamps of CTA 0
 };
 
 constexpr int kTileM = 128;   // query rows per MMA tile (TMEM lanes)

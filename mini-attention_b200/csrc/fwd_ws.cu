@@ -56,8 +56,8 @@ struct WsLayout {
   static constexpr int kBarKvFull = 2;                     // [kStages]
   static constexpr int kBarKvEmpty = kBarKvFull + kStages; // [kStages]
   static constexpr int kBarSFull = kBarKvEmpty + kStages;  // [2]  MMA -> softmax
-  static constexpr int kBarPReady = kBarSFull + 2;         // [2]  softmax -> MMA
-  static constexpr int kBarAlpha = kBarPReady + 2;         // [2]  softmax -> correction
+  static constexpr int kBarPReady = kBarSFull + 2;         // [2][2] softmax -> MMA, per half of P
+  static constexpr int kBarAlpha = kBarPReady + 4;         // [2]  softmax -> correction
   static constexpr int kBarOReady = kBarAlpha + 2;         // [2]  correction -> MMA
   static constexpr int kBarODone = kBarOReady + 2;         // [2]  MMA -> correction
   static constexpr int kBarLReady = kBarODone + 2;         // [2]  softmax -> correction (final l)
@@ -80,6 +80,17 @@ template <int N>
 __device__ __forceinline__ void reg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+#ifdef MA_TRACE
+constexpr int kTraceMax = 2048;
+#define MA_STAMP(role, tag)                                                              \
+  do {                                                                                   \
+    if (a.trace != nullptr && blockIdx.x == 0 && trace_n < kTraceMax)                    \
+      a.trace[(role) * kTraceMax + trace_n++] =                                          \
+          (static_cast<unsigned long long>(tag) << 48) | (clock64() & 0xFFFFFFFFFFFFull); \
+  } while (0)
+#else
+#define MA_STAMP(role, tag) do {} while (0)
+#endif
 __device__ __forceinline__ void warp_arrive(uint32_t bar) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
@@ -108,7 +119,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kOffMisc + 8);
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler
   const int lane = tid & 31;
 
   // ---- work item: heaviest (latest) Q tile pairs first; heads of one pair adjacent ----
@@ -140,7 +151,8 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar(L::kBarSFull + t), 1);
-      mbar_init(bar(L::kBarPReady + t), 4);
+      mbar_init(bar(L::kBarPReady + 2 * t), 4);
+      mbar_init(bar(L::kBarPReady + 2 * t + 1), 4);
       mbar_init(bar(L::kBarAlpha + t), 4);
       mbar_init(bar(L::kBarOReady + t), 4);
       mbar_init(bar(L::kBarODone + t), 1);
@@ -163,6 +175,9 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
   const WaitCtx wc{abort_flag, a.status, MINIATTN_WAIT_LIMIT_NS};
   const float c = a.scale_log2;
+#ifdef MA_TRACE
+  int trace_n = 0;
+#endif
 
   if (warp < 8) {
     // =========================== softmax ===========================================
@@ -182,27 +197,32 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       for (int j = 0; j < n_tiles; ++j) {
         mbar_wait(bar(L::kBarSFull + t), j & 1, wc, kErrWaitS);
         tc_fence_after();
+        if (r == 0) MA_STAMP(t, 1);
         uint32_t s[4][32];
 #pragma unroll
         for (int q = 0; q < 4; ++q) tmem_ld32(tS + q * 32, s[q]);
         tmem_wait_ld();
+        if (r == 0) MA_STAMP(t, 2);
 
         const int lim = vis_row - j * kTileN;
-        float mx = -INFINITY;
-        if (lim >= kTileN) {
+        if (lim < kTileN) {  // diagonal or ragged tile: hide the keys this row must not see
 #pragma unroll
           for (int q = 0; q < 4; ++q)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[q][i]));
-        } else {
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 32; ++i)
               if (q * 32 + i >= lim) s[q][i] = __float_as_uint(-INFINITY);
-              mx = fmaxf(mx, __uint_as_float(s[q][i]));
-            }
         }
+        // row maximum: four independent chains of 3-input max
+        float mx4[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float m = fmaxf(__uint_as_float(s[q][0]), __uint_as_float(s[q][1]));
+#pragma unroll
+          for (int i = 2; i < 32; i += 2)
+            m = fmax3(m, __uint_as_float(s[q][i]), __uint_as_float(s[q][i + 1]));
+          mx4[q] = m;
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         float alpha = 1.f;
         if (j == 0) {
           m_cur = mx;
@@ -215,6 +235,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         alpha_smem[t * kTileM + r] = alpha;
         warp_arrive(bar(L::kBarAlpha + t));
+        if (r == 0) MA_STAMP(t, 3);
 
         const float mc = (m_cur == -INFINITY) ? 0.f : m_cur * c;
         float psum0 = 0.f, psum1 = 0.f;
@@ -234,11 +255,15 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             }
           }
           tmem_st32(tS + hb * 32, pk);
+          // publish each half as soon as it is in TMEM: the PV MMAs of the first 64 keys
+          // run while the second half is still being exponentiated
+          tmem_wait_st();
+          tc_fence_before();
+          warp_arrive(bar(L::kBarPReady + 2 * t + hb));
+          if (r == 0) MA_STAMP(t, 4);
         }
         l_run = l_run * alpha + (psum0 + psum1);
-        tmem_wait_st();
-        tc_fence_before();
-        warp_arrive(bar(L::kBarPReady + t));
+        if (r == 0) MA_STAMP(t, 5);
       }
 
       l_smem[t * kTileM + r] = l_run;
@@ -256,6 +281,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     for (int j = 0; j < n_tiles; ++j) {
       for (int t = 0; t < nt; ++t) {
         mbar_wait(bar(L::kBarAlpha + t), j & 1, wc, kErrWaitCorr);
+        if (r == 0) MA_STAMP(2, 20 + t);
         const float alpha = alpha_smem[t * kTileM + r];
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
           mbar_wait(bar(L::kBarODone + t), (j - 1) & 1, wc, kErrWaitO);
@@ -274,6 +300,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tc_fence_before();
         }
         warp_arrive(bar(L::kBarOReady + t));
+        if (r == 0) MA_STAMP(2, 22 + t);
       }
     }
     // epilogue
@@ -332,6 +359,9 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     reg_dec<MA_REG_OTHER>();
     if (warp == 12) {
       // =========================== MMA issuer ======================================
+      // One thread issues every tcgen05.mma, strictly alternating the two Q tiles:
+      // PV0(j) S0(j+1) PV1(j) S1(j+1).  The alternation keeps the two softmax groups half a
+      // period apart, so one exponentiates while the other owns the tensor pipe.
       if (lane == 0 && n_tiles > 0) {
         constexpr uint32_t idesc_s = make_idesc(1, BF16 ? 1 : 0, 0, 0, kTileM, kTileN);
         constexpr uint32_t idesc_o = make_idesc(1, BF16 ? 1 : 0, 0, 1, kTileM, D);
@@ -364,17 +394,24 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const int kslot = cons % L::kStages;
           const uint32_t kpar = (cons / L::kStages) & 1;
           for (int t = 0; t < nt; ++t) {
-            mbar_wait(bar(L::kBarPReady + t), j & 1, wc, kErrWaitP);
+            MA_STAMP(3, 10 + t);
             mbar_wait(bar(L::kBarOReady + t), j & 1, wc, kErrWaitCorr);
-            tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < kTileN / 16; ++k) {
-              const uint64_t db =
-                  make_smem_desc(sRing + vslot * L::kTileBytes + k * 2048, kBoxBytes, 1024);
-              mma_f16_ts(tO[t], tS[t] + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+            for (int hb = 0; hb < 2; ++hb) {
+              mbar_wait(bar(L::kBarPReady + 2 * t + hb), j & 1, wc, kErrWaitP);
+              tc_fence_after();
+              MA_STAMP(3, 12 + 2 * hb + t);
+#pragma unroll
+              for (int kk = 0; kk < kTileN / 32; ++kk) {
+                const int k = hb * (kTileN / 32) + kk;
+                const uint64_t db =
+                    make_smem_desc(sRing + vslot * L::kTileBytes + k * 2048, kBoxBytes, 1024);
+                mma_f16_ts(tO[t], tS[t] + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+              }
             }
             mma_commit(bar(L::kBarODone + t));
             if (t == nt - 1) mma_commit(bar(L::kBarKvEmpty + vslot));
+            MA_STAMP(3, 18 + t);
             if (has_next) {
               if (t == 0) {
                 mbar_wait(bar(L::kBarKvFull + kslot), kpar, wc, kErrWaitKV);
@@ -382,6 +419,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               }
               issue_s(t, kslot);
               mma_commit(bar(L::kBarSFull + t));
+              MA_STAMP(3, 16 + t);
               if (t == nt - 1) mma_commit(bar(L::kBarKvEmpty + kslot));
             }
           }
