@@ -79,6 +79,28 @@ typedef struct MiniAttnFwdParams {
 int miniattn_fwd(const MiniAttnFwdParams* p, void* stream);
 
 /*
+ * Log-sum-exp merge of attention partials, used by the ring (context-parallel) launcher.
+ * No reference counterpart on the CUDA side; the arithmetic is the split-KV merge of
+ * kernels/standard/pytorch/benchmark_mla_decode_torch.py:244-272 applied to two partials:
+ *   m = max(lse_acc, lse_p); wa = e^(lse_acc-m); wb = e^(lse_p-m)
+ *   o_acc = (o_acc*wa + o_p*wb)/(wa+wb);  lse_acc = m + ln(wa+wb)
+ * All tensors are contiguous over `rows` = B*Hq*Nq query rows of D (64 or 128) elements.
+ */
+typedef struct MiniAttnMergeParams {
+  float*       acc_o;     /* [rows, D] fp32 running result, updated in place            */
+  float*       acc_lse;   /* [rows]    fp32 running log-sum-exp, updated in place       */
+  const void*  part_o;    /* [rows, D] 16-bit normalised partial of one ring step       */
+  const float* part_lse;  /* [rows]    its log-sum-exp (-inf = no visible key)          */
+  void*        out;       /* optional [rows, D] 16-bit: merged result, also written here */
+  int64_t rows;
+  int32_t D;
+  int32_t dtype;          /* dtype of part_o / out: MINIATTN_FP16 | MINIATTN_BF16       */
+  int32_t init;           /* 1: acc := partial (acc_o / acc_lse are not read)           */
+} MiniAttnMergeParams;
+
+int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream);
+
+/*
  * Failure-detection self-test (no reference counterpart; the reference never checks
  * its launches, flash_attention.cu:123).  Launches one CTA that waits on a barrier
  * nothing signals.  The wait gives up after `limit_ns` nanoseconds (0 < limit_ns <= 2e9),

@@ -20,6 +20,9 @@ cudaError_t launch_fwd_simple(int D, bool bf16, const CUtensorMap* tm, const Fwd
 cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
                           cudaStream_t st);
 cudaError_t launch_wait_selftest(int32_t* status, unsigned long long limit_ns, cudaStream_t st);
+cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part_o,
+                                  const float* part_lse, void* out, long long rows, int D, bool bf16,
+                                  int init, int sm_count, cudaStream_t st);
 }  // namespace ma
 
 namespace {
@@ -204,6 +207,31 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
     e = ma::launch_fwd_simple(p->D, p->dtype == MINIATTN_BF16, tm, a, st);
   else
     e = ma::launch_fwd_ws(p->D, p->dtype == MINIATTN_BF16, tm, a, sms, st);
+  if (e != cudaSuccess)
+    return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return MINIATTN_OK;
+}
+
+int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream) {
+  g_err[0] = 0;
+  if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
+  if (p->rows < 0) return fail(MINIATTN_EINVAL, "negative row count");
+  if (p->D != 64 && p->D != 128)
+    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64 or 128)", p->D);
+  if (p->dtype != MINIATTN_FP16 && p->dtype != MINIATTN_BF16)
+    return fail(MINIATTN_EUNSUPPORTED, "dtype must be fp16 (0) or bf16 (1), got %d", p->dtype);
+  if (p->init != 0 && p->init != 1) return fail(MINIATTN_EINVAL, "init must be 0 or 1");
+  if (p->rows == 0) return MINIATTN_OK;
+  if (!p->acc_o || !p->acc_lse || !p->part_o || !p->part_lse)
+    return fail(MINIATTN_EINVAL, "acc_o, acc_lse, part_o and part_lse must not be null");
+  if (reinterpret_cast<uintptr_t>(p->acc_o) % 16 || reinterpret_cast<uintptr_t>(p->part_o) % 16 ||
+      (p->out && reinterpret_cast<uintptr_t>(p->out) % 16))
+    return fail(MINIATTN_EINVAL, "acc_o, part_o and out must be 16-byte aligned");
+  int sms = 0, major = 0, rc;
+  if ((rc = device_sm_count(&sms, &major)) != 0) return rc;
+  cudaError_t e = ma::launch_merge_partials(p->acc_o, p->acc_lse, p->part_o, p->part_lse, p->out,
+                                            p->rows, p->D, p->dtype == MINIATTN_BF16, p->init, sms,
+                                            reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;

@@ -32,6 +32,16 @@ class FwdParams(C.Structure):
     ]
 
 
+class MergeParams(C.Structure):
+    """Mirror of ``MiniAttnMergeParams``."""
+
+    _fields_ = [
+        ("acc_o", C.c_void_p), ("acc_lse", C.c_void_p), ("part_o", C.c_void_p),
+        ("part_lse", C.c_void_p), ("out", C.c_void_p),
+        ("rows", C.c_int64), ("D", C.c_int32), ("dtype", C.c_int32), ("init", C.c_int32),
+    ]
+
+
 def _load() -> C.CDLL:
     if not _LIB_PATH.exists():
         raise ImportError(
@@ -41,6 +51,8 @@ def _load() -> C.CDLL:
     lib = C.CDLL(str(_LIB_PATH))
     lib.miniattn_fwd.argtypes = [C.POINTER(FwdParams), C.c_void_p]
     lib.miniattn_fwd.restype = C.c_int
+    lib.miniattn_merge_partials.argtypes = [C.POINTER(MergeParams), C.c_void_p]
+    lib.miniattn_merge_partials.restype = C.c_int
     lib.miniattn_selftest_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     lib.miniattn_selftest_wait.restype = C.c_int
     lib.miniattn_version.restype = C.c_char_p

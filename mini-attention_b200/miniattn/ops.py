@@ -135,6 +135,48 @@ def flash_attn_fwd(
     return (out, lse) if return_lse else out
 
 
+def merge_partials(
+    acc_o: torch.Tensor,
+    acc_lse: torch.Tensor,
+    part_o: torch.Tensor,
+    part_lse: torch.Tensor,
+    *,
+    init: bool = False,
+    out: Optional[torch.Tensor] = None,
+) -> None:
+    """In-place log-sum-exp merge of one ring-step partial into the running result.
+
+    acc_o fp32 (..., N, D) and acc_lse fp32 (..., N) are updated; part_o is the fp16/bf16
+    normalised partial with its part_lse.  ``init=True`` overwrites the accumulators with the
+    partial; ``out`` (same dtype as part_o) additionally receives the merged result.  All
+    tensors must be contiguous CUDA tensors of matching shapes.
+    """
+    if part_o.dtype not in _DTYPES:
+        raise RuntimeError("Only fp16 and bf16 partials are supported")
+    if acc_o.dtype != torch.float32 or acc_lse.dtype != torch.float32 or part_lse.dtype != torch.float32:
+        raise RuntimeError("acc_o, acc_lse and part_lse must be fp32")
+    tensors = [acc_o, acc_lse, part_o, part_lse] + ([out] if out is not None else [])
+    for t in tensors:
+        if not t.is_cuda or not t.is_contiguous() or t.device != acc_o.device:
+            raise RuntimeError("merge_partials takes contiguous CUDA tensors on one device")
+    if acc_o.shape != part_o.shape or acc_lse.shape != part_lse.shape or acc_lse.shape != acc_o.shape[:-1]:
+        raise RuntimeError("shape mismatch between accumulators and partials")
+    if out is not None and (out.shape != part_o.shape or out.dtype != part_o.dtype):
+        raise RuntimeError("out must match part_o in shape and dtype")
+    p = _lib.MergeParams()
+    p.acc_o, p.acc_lse = acc_o.data_ptr(), acc_lse.data_ptr()
+    p.part_o, p.part_lse = part_o.data_ptr(), part_lse.data_ptr()
+    p.out = out.data_ptr() if out is not None else None
+    p.rows = acc_lse.numel()
+    p.D = acc_o.shape[-1]
+    p.dtype = _DTYPES[part_o.dtype]
+    p.init = 1 if init else 0
+    with torch.cuda.device(acc_o.device):
+        stream = torch.cuda.current_stream(acc_o.device).cuda_stream
+        rc = _lib.lib.miniattn_merge_partials(C.byref(p), C.c_void_p(stream))
+    _lib.check(rc, "miniattn_merge_partials")
+
+
 def selftest_wait(limit_ms: float = 50.0, device: Union[torch.device, str, None] = None) -> int:
     """Run the bounded-wait self-test kernel; returns the status word it produced."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
