@@ -10,6 +10,10 @@ Workloads (``--workload``):
                 B=2 shard of a batch of 2*N (sharded by batch x head, no communication): weak scaling.
   c3            GQA causal bf16 B=4 Hq=32 Hkv=8 N=4096 D=128, the (batch x KV-head) groups split
                 across the ranks, no communication: strong scaling.
+  c5            causal MHA fp16 B=1 H=32 N=131072 D=128 in ring / context-parallel mode: zig-zag
+                sequence split, K/V pairs travel over NCCL send/recv while the resident Q blocks
+                attend to the visiting pair, log-sum-exp merge of the partials: strong scaling.
+                (--seq-len overrides N for quick checks.)
 
 A step is one forward pass over one batch.  ``value`` is TFLOPS (4*B*H*N^2*D flops, halved for
 causal) with inputs resident in HBM, timed with CUDA events on the launch stream; L2 is flushed
@@ -42,6 +46,8 @@ WORKLOADS = {
                name="MHA fwd non-causal fp16 B=2 H=8 N=8192 D=128 (top of the N=512..8192 sweep)"),
     "c3": dict(B=4, Hq=32, Hkv=8, N=4096, D=128, dtype="bf16", causal=True,
                name="GQA fwd causal bf16 B=4 Hq=32 Hkv=8 N=4096 D=128, (batch x KV-head) groups sharded"),
+    "c5": dict(B=1, Hq=32, Hkv=32, N=131072, D=128, dtype="fp16", causal=True,
+               name="long-context causal MHA fwd fp16 B=1 H=32 N=131072 D=128, zig-zag ring over the GPUs"),
 }
 SWEEP_N = (512, 1024, 2048, 4096)
 METRIC = "attention fwd TFLOPS (fp16, D=128, N=512-8192) and % of B200 dense peak"
@@ -118,9 +124,11 @@ def cpu_attention_sample(w, budget_s: float):
     torch.set_num_threads(cores)
     dt = torch.float16 if w["dtype"] == "fp16" else torch.bfloat16
     G = w["Hq"] // w["Hkv"]
-    # one KV-head group (G query heads sharing one KV head) of one batch element per unit
-    q, k, v = make_inputs(1, G, 1, w["N"], w["N"], w["D"], dt, seed=0)
-    unit_flops = flops(1, G, w["N"], w["D"], w["causal"])
+    # one KV-head group (G query heads sharing one KV head) of one batch element per unit;
+    # very long sequences are sampled at N=16384 (the N x N score matrix must fit in host memory)
+    n_cpu = min(w["N"], 16384)
+    q, k, v = make_inputs(1, G, 1, n_cpu, n_cpu, w["D"], dt, seed=0)
+    unit_flops = flops(1, G, n_cpu, w["D"], w["causal"])
     total_units = w["B"] * w["Hkv"]
 
     def sdpa():  # the reference test's call (tests/test_correctness.py:35-43), GQA by expand
@@ -145,7 +153,8 @@ def cpu_attention_sample(w, budget_s: float):
             best = (tf, name, reps)
     tf, name, reps = best
     desc = (f"{name} on CPU, {reps} of {total_units} (batch x KV-head) units of the workload "
-            f"(each {G} query head(s) x N={w['N']}), {cores} threads")
+            f"(each {G} query head(s) x N={n_cpu}" + (f", sampled below the workload's N={w['N']}" if n_cpu != w["N"] else "")
+            + f"), {cores} threads")
     return tf, cores, desc
 
 
@@ -185,11 +194,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--kernel", default="auto")
+    ap.add_argument("--seq-len", type=int, default=0, help="override the workload's sequence length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the one-shot timings of the smaller N")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
+    if args.seq_len:
+        w["N"] = args.seq_len
+        w["name"] += f" [N overridden to {args.seq_len}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -210,6 +223,7 @@ def main():
 
     dt = torch.float16 if w["dtype"] == "fp16" else torch.bfloat16
     B, Hq, Hkv, N, D, causal = w["B"], w["Hq"], w["Hkv"], w["N"], w["D"], w["causal"]
+    ring = args.workload == "c5"
     if args.workload == "c3":
         # strong scaling: split the B*Hkv groups (whole groups stay on one GPU); per-rank tensors
         # are (1, G*groups, N, D) / (1, groups, N, D)
@@ -217,34 +231,50 @@ def main():
         assert groups % world == 0, "group count must divide by the number of GPUs"
         per = groups // world
         G = Hq // Hkv
-        shard = dict(B=1, Hq=per * G, Hkv=per)
+        shard = dict(B=1, Hq=per * G, Hkv=per, N=N)
+        scaling = "strong"
+        total_flops = flops(B, Hq, N, D, causal)
+    elif ring:
+        assert N % (2 * world * 128) == 0, "sequence must split into 2*world blocks of whole tiles"
+        shard = dict(B=B, Hq=Hq, Hkv=Hkv, N=N // world)  # this rank's two zig-zag blocks
         scaling = "strong"
         total_flops = flops(B, Hq, N, D, causal)
     else:
-        shard = dict(B=B, Hq=Hq, Hkv=Hkv)
+        shard = dict(B=B, Hq=Hq, Hkv=Hkv, N=N)
         scaling = "weak"
         total_flops = flops(B, Hq, N, D, causal) * world
-    sB, sHq, sHkv = shard["B"], shard["Hq"], shard["Hkv"]
-    step_flops = flops(sB, sHq, N, D, causal)
+    sB, sHq, sHkv, sN = shard["B"], shard["Hq"], shard["Hkv"], shard["N"]
+    step_flops = total_flops / world if ring else flops(sB, sHq, N, D, causal)
 
     g = torch.Generator().manual_seed(1234 + rank)
-    hq = torch.randn(sB, sHq, N, D, generator=g).to(dt).pin_memory()
-    hk = torch.randn(sB, sHkv, N, D, generator=g).to(dt).pin_memory()
-    hv = torch.randn(sB, sHkv, N, D, generator=g).to(dt).pin_memory()
+    hq = torch.randn(sB, sHq, sN, D, generator=g).to(dt).pin_memory()
+    hk = torch.randn(sB, sHkv, sN, D, generator=g).to(dt).pin_memory()
+    hv = torch.randn(sB, sHkv, sN, D, generator=g).to(dt).pin_memory()
     ho = torch.empty_like(hq).pin_memory()
     q, k, v = hq.to(dev), hk.to(dev), hv.to(dev)
     o = torch.empty_like(q)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
+    launches_per_step = 1
+    if ring:
+        from miniattn import parallel as par
+        n_tasks = sum(len(par.ring_step_tasks(rank, world, s_, causal)) for s_ in range(world))
+        launches_per_step = 2 * n_tasks  # one attention + one merge launch per task
+
+        def attend():
+            o.copy_(par.ring_forward(q, k, v, causal=causal, rank=rank, world=world))
+    else:
+        def attend():
+            miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel)
 
     def step_device():
-        miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel)
+        attend()
 
     def step_e2e():
         q.copy_(hq, non_blocking=True)
         k.copy_(hk, non_blocking=True)
         v.copy_(hv, non_blocking=True)
-        miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel)
+        attend()
         ho.copy_(o, non_blocking=True)
 
     def barrier():
@@ -309,20 +339,21 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu": shard, "seq_len": N, "head_dim": D, "causal": causal,
-                       "parallelism": f"batch x head shards over {world} GPU(s), no communication",
+                       "parallelism": (f"zig-zag ring over {world} GPU(s): NCCL send/recv of K/V pairs + LSE merge" if ring
+                                       else f"batch x head shards over {world} GPU(s), no communication"),
                        "l2": "flushed between steps (256 MiB write outside the timed intervals)",
                        "timing": "sum of per-step CUDA-event intervals on the launch stream, max over ranks"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "peak_source": peak_src, "frac_of_nominal_2250": achieved / 2250.0,
-                         "algorithmic_flops_per_launch": step_flops,
-                         "algorithmic_hbm_bytes_per_launch": (2 * sHq + 2 * sHkv) * sB * N * D * 2,
-                         "hbm_gbs": (2 * sHq + 2 * sHkv) * sB * N * D * 2 / ms_dev / 1e6},
+                         "algorithmic_flops_per_step": step_flops,
+                         "algorithmic_hbm_bytes_per_step": (2 * sHq + 2 * sHkv) * sB * sN * D * 2,
+                         "hbm_gbs": (2 * sHq + 2 * sHkv) * sB * sN * D * 2 / ms_dev / 1e6},
             "e2e": None if args.no_e2e else {
                 "value": total_flops / ms_e2e / 1e9, "unit": "TFLOPS", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": hq.numel() * 2 + hk.numel() * 2 + hv.numel() * 2,
                 "d2h_bytes_per_step": ho.numel() * 2},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * launches_per_step,
             "clocks": clocks,
             "device_status": status,
             "kernel": args.kernel,
