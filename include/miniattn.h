@@ -79,6 +79,37 @@ typedef struct MiniAttnFwdParams {
 int miniattn_fwd(const MiniAttnFwdParams* p, void* stream);
 
 /*
+ * INT8-QK variant (SageAttention-style; the reference holds no code for it, only its task
+ * configuration states the recipe): K is smoothed by subtracting its per-channel mean over
+ * tokens, Q and the smoothed K are quantised to int8 with one symmetric fp32 scale per block of
+ * 128 tokens, S = Q8 K8^T runs on tcgen05 kind::i8 with int32 accumulation and is de-quantised
+ * inside the softmax; P V stays 16 bit with fp32 accumulation.
+ *
+ * `fwd` carries q, k, v, o, sizes, strides, dtype, causal and softmax_scale exactly as for
+ * miniattn_fwd (lse and status are honoured too; q_pos0 / k_pos0 shift the causal diagonal).
+ * The remaining members are caller-allocated device buffers:
+ *   q8       [B, Hq,  Nq, D] int8, contiguous         k8      [B, Hkv, Nk, D] int8, contiguous
+ *   q_scale  [B, Hq,  ceil(Nq/128)] fp32 (softmax_scale*log2(e) folded in)
+ *   k_scale  [B, Hkv, ceil(Nk/128)] fp32
+ *   k_partial  scratch, B*Hkv*ceil(Nk/1024)*D floats (column sums of K, pre-pass only)
+ *   k_mean   optional [B, Hkv, D] fp32 output of the pre-pass
+ * miniattn_quant_qk_int8 runs the pre-pass (fills q8, k8, q_scale, k_scale);
+ * miniattn_fwd_int8qk runs the attention kernel on buffers the pre-pass filled.
+ */
+typedef struct MiniAttnInt8Params {
+  MiniAttnFwdParams fwd;
+  int8_t* q8;
+  int8_t* k8;
+  float*  q_scale;
+  float*  k_scale;
+  float*  k_partial;
+  float*  k_mean;
+} MiniAttnInt8Params;
+
+int miniattn_quant_qk_int8(const MiniAttnInt8Params* p, void* stream);
+int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream);
+
+/*
  * Log-sum-exp merge of attention partials, used by the ring (context-parallel) launcher.
  * No reference counterpart on the CUDA side; the arithmetic is the split-KV merge of
  * kernels/standard/pytorch/benchmark_mla_decode_torch.py:244-272 applied to two partials:

@@ -19,6 +19,12 @@ cudaError_t launch_fwd_simple(int D, bool bf16, const CUtensorMap* tm, const Fwd
                               cudaStream_t st);
 cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
                           cudaStream_t st);
+cudaError_t launch_fwd_ws_int8qk(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
+                                 cudaStream_t st);
+cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs, const void* k,
+                            const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk, float q_fold,
+                            int8_t* q8, int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
+                            cudaStream_t st);
 cudaError_t launch_wait_selftest(int32_t* status, unsigned long long limit_ns, cudaStream_t st);
 cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part_o,
                                   const float* part_lse, void* out, long long rows, int D, bool bf16,
@@ -64,7 +70,7 @@ EncodeTiledFn encode_fn() {
 // (one 128-byte swizzled row per token).
 int make_map(CUtensorMap* out, const void* base, int elem_bytes, CUtensorMapDataType dt, int D,
              int N, int H, int B, const int64_t stride[3], int box_cols, int box_rows,
-             const char* what) {
+             const char* what, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return fail(MINIATTN_ECUDA, "cuTensorMapEncodeTiled entry point not found");
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
@@ -76,7 +82,7 @@ int make_map(CUtensorMap* out, const void* base, int elem_bytes, CUtensorMapData
   for (int i = 0; i < 3; ++i)
     if (dims[i + 1] == 1) strides[i] = (cuuint64_t)D * elem_bytes;
   CUresult r = enc(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(MINIATTN_ECUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
@@ -124,8 +130,8 @@ const char* miniattn_version(void) { return "miniattn-b200 0.1 sm_100a"; }
 
 const char* miniattn_last_error_string(void) { return g_err; }
 
-int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
-  g_err[0] = 0;
+// Shared argument checks of the forward entry points.  Returns 1 when there is nothing to do.
+static int check_fwd_params(const MiniAttnFwdParams* p) {
   if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
   if (p->dtype != MINIATTN_FP16 && p->dtype != MINIATTN_BF16)
     return fail(MINIATTN_EUNSUPPORTED, "dtype must be fp16 (0) or bf16 (1), got %d", p->dtype);
@@ -133,7 +139,7 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
     return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64 or 128)", p->D);
   if (p->B < 0 || p->Hq < 0 || p->Hkv < 0 || p->Nq < 0 || p->Nk < 0)
     return fail(MINIATTN_EINVAL, "negative size");
-  if (p->B == 0 || p->Hq == 0 || p->Nq == 0) return MINIATTN_OK;  // empty output: nothing to do
+  if (p->B == 0 || p->Hq == 0 || p->Nq == 0) return 1;  // empty output: nothing to do
   if (p->Hkv == 0 || p->Hq % p->Hkv != 0)
     return fail(MINIATTN_EINVAL, "Hq (%d) must be a positive multiple of Hkv (%d)", p->Hq, p->Hkv);
   if (p->Hq > 65535 || p->B > 65535)
@@ -152,12 +158,48 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
     if ((rc = check_tensor(p->v, p->v_stride, p->D, "v")) != 0) return rc;
   }
 
-  int sms = 0, major = 0;
-  if ((rc = device_sm_count(&sms, &major)) != 0) return rc;
+  return MINIATTN_OK;
+}
+
+static void fill_args(const MiniAttnFwdParams* p, ma::FwdArgs* a) {
+  a->lse = p->lse;
+  a->status = p->status;
+  a->q_pos0 = p->q_pos0;
+  a->k_pos0 = p->k_pos0;
+  a->Nq = p->Nq;
+  a->Nk = p->Nk;
+  a->Hq = p->Hq;
+  a->Hkv = p->Hkv;
+  a->B = p->B;
+  a->causal = p->causal;
+  a->scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)p->D);
+  a->scale_log2 = a->scale * 1.4426950408889634f;
+  a->n_q_tiles = (p->Nq + ma::kTileM - 1) / ma::kTileM;
+  a->sq = nullptr;
+  a->sk = nullptr;
+  a->trace = nullptr;
+#ifdef MA_TRACE
+  a->trace = g_trace;
+#endif
+}
+
+static int check_device(int* sms) {
+  int major = 0, rc;
+  if ((rc = device_sm_count(sms, &major)) != 0) return rc;
   if (major != 10)
     return fail(MINIATTN_EUNSUPPORTED,
                 "this library holds sm_100a code only; current device has compute capability %d.x",
                 major);
+  return MINIATTN_OK;
+}
+
+int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
+  g_err[0] = 0;
+  int rc = check_fwd_params(p);
+  if (rc != 0) return rc > 0 ? MINIATTN_OK : rc;
+  const bool has_keys = p->Nk > 0;
+  int sms = 0;
+  if ((rc = check_device(&sms)) != 0) return rc;
 
   const CUtensorMapDataType dt =
       p->dtype == MINIATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -181,23 +223,7 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
     return rc;
 
   ma::FwdArgs a;
-  a.lse = p->lse;
-  a.status = p->status;
-  a.q_pos0 = p->q_pos0;
-  a.k_pos0 = p->k_pos0;
-  a.Nq = p->Nq;
-  a.Nk = p->Nk;
-  a.Hq = p->Hq;
-  a.Hkv = p->Hkv;
-  a.B = p->B;
-  a.causal = p->causal;
-  a.scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)p->D);
-  a.scale_log2 = a.scale * 1.4426950408889634f;
-  a.n_q_tiles = (p->Nq + ma::kTileM - 1) / ma::kTileM;
-  a.trace = nullptr;
-#ifdef MA_TRACE
-  a.trace = g_trace;
-#endif
+  fill_args(p, &a);
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int kernel = p->kernel;
@@ -207,6 +233,84 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
     e = ma::launch_fwd_simple(p->D, p->dtype == MINIATTN_BF16, tm, a, st);
   else
     e = ma::launch_fwd_ws(p->D, p->dtype == MINIATTN_BF16, tm, a, sms, st);
+  if (e != cudaSuccess)
+    return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return MINIATTN_OK;
+}
+
+static int check_int8_params(const MiniAttnInt8Params* p, bool need_v) {
+  if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
+  MiniAttnFwdParams f = p->fwd;
+  if (!need_v) {  // the pre-pass reads q and k only
+    f.v = f.k;
+    for (int i = 0; i < 3; ++i) f.v_stride[i] = f.k_stride[i];
+    if (f.o == nullptr) {
+      f.o = const_cast<void*>(f.q);
+      for (int i = 0; i < 3; ++i) f.o_stride[i] = f.q_stride[i];
+    }
+  }
+  int rc = check_fwd_params(&f);
+  if (rc != 0) return rc;
+  if (p->fwd.Nk == 0) return fail(MINIATTN_EINVAL, "the INT8-QK variant needs at least one key");
+  if (!p->q8 || !p->k8 || !p->q_scale || !p->k_scale)
+    return fail(MINIATTN_EINVAL, "q8, k8, q_scale and k_scale must not be null");
+  if (reinterpret_cast<uintptr_t>(p->q8) % 16 || reinterpret_cast<uintptr_t>(p->k8) % 16)
+    return fail(MINIATTN_EINVAL, "q8 and k8 must be 16-byte aligned");
+  return MINIATTN_OK;
+}
+
+int miniattn_quant_qk_int8(const MiniAttnInt8Params* p, void* stream) {
+  g_err[0] = 0;
+  int rc = check_int8_params(p, false);
+  if (rc != 0) return rc > 0 ? MINIATTN_OK : rc;
+  if (!p->k_partial) return fail(MINIATTN_EINVAL, "k_partial scratch must not be null");
+  int sms = 0;
+  if ((rc = check_device(&sms)) != 0) return rc;
+  const MiniAttnFwdParams& f = p->fwd;
+  const float scale = f.softmax_scale > 0.f ? f.softmax_scale : 1.0f / sqrtf((float)f.D);
+  const long long qs[3] = {f.q_stride[0], f.q_stride[1], f.q_stride[2]};
+  const long long ks[3] = {f.k_stride[0], f.k_stride[1], f.k_stride[2]};
+  cudaError_t e = ma::launch_quant_qk(f.D, f.dtype == MINIATTN_BF16, f.q, qs, f.k, ks, f.B, f.Hq, f.Hkv,
+                                      f.Nq, f.Nk, scale * 1.4426950408889634f, p->q8, p->k8, p->q_scale,
+                                      p->k_scale, p->k_partial, p->k_mean,
+                                      reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess)
+    return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return MINIATTN_OK;
+}
+
+int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream) {
+  g_err[0] = 0;
+  int rc = check_int8_params(p, true);
+  if (rc != 0) return rc > 0 ? MINIATTN_OK : rc;
+  int sms = 0;
+  if ((rc = check_device(&sms)) != 0) return rc;
+  const MiniAttnFwdParams& f = p->fwd;
+  const CUtensorMapDataType dt =
+      f.dtype == MINIATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  // int8 rows are D bytes wide: one box per tile, 64-byte swizzle at D=64, 128-byte at D=128
+  const CUtensorMapSwizzle sw8 = f.D == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  const int64_t q8s[3] = {(int64_t)f.Hq * f.Nq * f.D, (int64_t)f.Nq * f.D, f.D};
+  const int64_t k8s[3] = {(int64_t)f.Hkv * f.Nk * f.D, (int64_t)f.Nk * f.D, f.D};
+  CUtensorMap tm[4];
+  if ((rc = make_map(&tm[0], p->q8, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8, f.D, f.Nq, f.Hq, f.B, q8s, f.D,
+                     ma::kTileM, "q8", sw8)) != 0)
+    return rc;
+  if ((rc = make_map(&tm[1], p->k8, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8, f.D, f.Nk, f.Hkv, f.B, k8s, f.D,
+                     ma::kTileN, "k8", sw8)) != 0)
+    return rc;
+  if ((rc = make_map(&tm[2], f.v, 2, dt, f.D, f.Nk, f.Hkv, f.B, f.v_stride, ma::kBoxCols, ma::kTileN,
+                     "v")) != 0)
+    return rc;
+  if ((rc = make_map(&tm[3], f.o, 2, dt, f.D, f.Nq, f.Hq, f.B, f.o_stride, ma::kBoxCols, ma::kTileM,
+                     "o")) != 0)
+    return rc;
+  ma::FwdArgs a;
+  fill_args(&f, &a);
+  a.sq = p->q_scale;
+  a.sk = p->k_scale;
+  cudaError_t e = ma::launch_fwd_ws_int8qk(f.D, f.dtype == MINIATTN_BF16, tm, a,
+                                           reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;
@@ -227,8 +331,8 @@ int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream) {
   if (reinterpret_cast<uintptr_t>(p->acc_o) % 16 || reinterpret_cast<uintptr_t>(p->part_o) % 16 ||
       (p->out && reinterpret_cast<uintptr_t>(p->out) % 16))
     return fail(MINIATTN_EINVAL, "acc_o, part_o and out must be 16-byte aligned");
-  int sms = 0, major = 0, rc;
-  if ((rc = device_sm_count(&sms, &major)) != 0) return rc;
+  int sms = 0, rc;
+  if ((rc = check_device(&sms)) != 0) return rc;
   cudaError_t e = ma::launch_merge_partials(p->acc_o, p->acc_lse, p->part_o, p->part_lse, p->out,
                                             p->rows, p->D, p->dtype == MINIATTN_BF16, p->init, sms,
                                             reinterpret_cast<cudaStream_t>(stream));

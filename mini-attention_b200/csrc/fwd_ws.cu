@@ -98,7 +98,10 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar) {
 
 }  // namespace
 
-template <int D, bool BF16>
+// QK8: Q and K arrive as int8 (one fp32 scale per 128-token block, softmax scale * log2e folded
+// into the Q scales); S = Q8 K8^T runs on tcgen05 kind::i8 with an int32 accumulator and is
+// de-quantised on the fly in the softmax; P, V and the PV MMA stay 16 bit.
+template <int D, bool BF16, bool QK8>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -191,8 +194,15 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       long long vis_ll = a.Nk;
       if (a.causal) vis_ll = min(vis_ll, a.q_pos0 + row - a.k_pos0 + 1);
       const int vis_row = static_cast<int>(max(0ll, vis_ll));
-      float m_cur = -INFINITY;
+      float m_cur = -INFINITY;  // running (lazily updated) row maximum, log2 units
       float l_run = 0.f;
+      float sq_t = 0.f, sk_next = 0.f;
+      const float* sk_row = nullptr;
+      if constexpr (QK8) {
+        sq_t = __ldg(a.sq + (static_cast<long long>(b) * a.Hq + h) * a.n_q_tiles + (pair * 2 + t));
+        sk_row = a.sk + (static_cast<long long>(b) * a.Hkv + hk) * ((a.Nk + kTileN - 1) / kTileN);
+        if (n_tiles > 0) sk_next = __ldg(sk_row);
+      }
 
       for (int j = 0; j < n_tiles; ++j) {
         mbar_wait(bar(L::kBarSFull + t), j & 1, wc, kErrWaitS);
@@ -204,6 +214,20 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tmem_wait_ld();
         if (r == 0) MA_STAMP(t, 2);
 
+        // cj turns a raw score into log2 units: softmax scale * log2e, times the two
+        // de-quantisation scales of this (Q block, K block) for the int8 variant.
+        float cj = c;
+        if constexpr (QK8) {
+          cj = sq_t * sk_next;
+          if (j + 1 < n_tiles) sk_next = __ldg(sk_row + j + 1);
+          // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding the
+          // bit pattern of 1.5*2^23 and subtracting that value is exact.
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              s[q][i] = __float_as_uint(__uint_as_float(s[q][i] + 0x4B400000u) - 12582912.f);
+        }
         const int lim = vis_row - j * kTileN;
         if (lim < kTileN) {  // diagonal or ragged tile: hide the keys this row must not see
 #pragma unroll
@@ -222,14 +246,15 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             m = fmax3(m, __uint_as_float(s[q][i]), __uint_as_float(s[q][i + 1]));
           mx4[q] = m;
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // running maximum m_cur is kept in log2 units (raw maximum * cj)
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * cj;
         float alpha = 1.f;
         if (j == 0) {
           m_cur = mx;
         } else {
           const float m_new = fmaxf(m_cur, mx);
-          if ((m_new - m_cur) * c > kLazyThreshold) {  // also taken when m_cur = -inf
-            alpha = ex2((m_cur - m_new) * c);
+          if (m_new - m_cur > kLazyThreshold) {  // also taken when m_cur = -inf
+            alpha = ex2(m_cur - m_new);
             m_cur = m_new;
           }
         }
@@ -237,7 +262,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         warp_arrive(bar(L::kBarAlpha + t));
         if (r == 0) MA_STAMP(t, 3);
 
-        const float mc = (m_cur == -INFINITY) ? 0.f : m_cur * c;
+        const float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
         float psum0 = 0.f, psum1 = 0.f;
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {  // 64 keys -> 32 packed columns per TMEM store
@@ -247,8 +272,8 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const int q = hb * 2 + qq;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float p0 = ex2(fmaf(__uint_as_float(s[q][i]), c, -mc));
-              const float p1 = ex2(fmaf(__uint_as_float(s[q][i + 1]), c, -mc));
+              const float p0 = ex2(fmaf(__uint_as_float(s[q][i]), cj, -mc));
+              const float p1 = ex2(fmaf(__uint_as_float(s[q][i + 1]), cj, -mc));
               psum0 += p0;
               psum1 += p1;
               pk[qq * 16 + (i >> 1)] = pack2<BF16>(p0, p1);
@@ -269,7 +294,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       l_smem[t * kTileM + r] = l_run;
       warp_arrive(bar(L::kBarLReady + t));
       if (a.lse != nullptr && row < a.Nq) {
-        const float lse = (l_run > 0.f) ? (m_cur * a.scale + __logf(l_run)) : -INFINITY;
+        const float lse = (l_run > 0.f) ? (m_cur * 0.6931471805599453f + __logf(l_run)) : -INFINITY;
         a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] = lse;
       }
     }
@@ -363,17 +388,32 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // PV0(j) S0(j+1) PV1(j) S1(j+1).  The alternation keeps the two softmax groups half a
       // period apart, so one exponentiates while the other owns the tensor pipe.
       if (lane == 0 && n_tiles > 0) {
-        constexpr uint32_t idesc_s = make_idesc(1, BF16 ? 1 : 0, 0, 0, kTileM, kTileN);
+        // kind::f16: D fmt f32, A/B f16 or bf16.  kind::i8: D fmt s32 (2), A/B signed int8 (1).
+        constexpr uint32_t idesc_s =
+            QK8 ? make_idesc(2, 1, 0, 0, kTileM, kTileN) : make_idesc(1, BF16 ? 1 : 0, 0, 0, kTileM, kTileN);
         constexpr uint32_t idesc_o = make_idesc(1, BF16 ? 1 : 0, 0, 1, kTileM, D);
         const uint32_t tS[2] = {tmem_base + L::kColS0, tmem_base + L::kColS1};
         const uint32_t tO[2] = {tmem_base + L::kColO0, tmem_base + L::kColO1};
         auto issue_s = [&](int t, int slot) {
+          if constexpr (QK8) {
+            // int8 rows are D bytes: 64-byte swizzle (8 rows = 512 B) at D=64, 128-byte at D=128;
+            // one MMA consumes K = 32 bytes.
+            constexpr uint32_t kLayout = (D == 64) ? 4u : 2u;
+            constexpr uint32_t kSbo = (D == 64) ? 512u : 1024u;
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = (k / 4) * kBoxBytes + (k % 4) * 32;
-            const uint64_t da = make_smem_desc(sQ + t * L::kTileBytes + off, 16, 1024);
-            const uint64_t db = make_smem_desc(sRing + slot * L::kTileBytes + off, 16, 1024);
-            mma_f16_ss(tS[t], da, db, idesc_s, k > 0);
+            for (int k = 0; k < D / 32; ++k) {
+              const uint64_t da = make_smem_desc(sQ + t * L::kTileBytes + k * 32, 16, kSbo, kLayout);
+              const uint64_t db = make_smem_desc(sRing + slot * L::kTileBytes + k * 32, 16, kSbo, kLayout);
+              mma_i8_ss(tS[t], da, db, idesc_s, k > 0);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+              const uint32_t off = (k / 4) * kBoxBytes + (k % 4) * 32;
+              const uint64_t da = make_smem_desc(sQ + t * L::kTileBytes + off, 16, 1024);
+              const uint64_t db = make_smem_desc(sRing + slot * L::kTileBytes + off, 16, 1024);
+              mma_f16_ss(tS[t], da, db, idesc_s, k > 0);
+            }
           }
         };
         for (int t = 0; t < nt; ++t) mbar_wait(bar(L::kBarQFull + t), 0, wc, kErrWaitKV);
@@ -431,11 +471,16 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // =========================== TMA producer ====================================
       if (lane == 0 && n_tiles > 0) {
         for (int t = 0; t < nt; ++t) {
-          mbar_expect_tx(bar(L::kBarQFull + t), L::kTileBytes);
+          if constexpr (QK8) {  // one box of D bytes x 128 rows
+            mbar_expect_tx(bar(L::kBarQFull + t), kTileM * D);
+            tma_load_4d(sQ + t * L::kTileBytes, &tm_q, bar(L::kBarQFull + t), 0, q0 + t * kTileM, h, b);
+          } else {
+            mbar_expect_tx(bar(L::kBarQFull + t), L::kTileBytes);
 #pragma unroll
-          for (int bx = 0; bx < L::kBoxes; ++bx)
-            tma_load_4d(sQ + t * L::kTileBytes + bx * kBoxBytes, &tm_q, bar(L::kBarQFull + t),
-                        bx * kBoxCols, q0 + t * kTileM, h, b);
+            for (int bx = 0; bx < L::kBoxes; ++bx)
+              tma_load_4d(sQ + t * L::kTileBytes + bx * kBoxBytes, &tm_q, bar(L::kBarQFull + t),
+                          bx * kBoxCols, q0 + t * kTileM, h, b);
+          }
         }
         const int n_fill = 2 * n_tiles;
         for (int i = 0; i < n_fill; ++i) {
@@ -443,13 +488,18 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const int use = i / L::kStages;
           if (use > 0) mbar_wait(bar(L::kBarKvEmpty + slot), (use - 1) & 1, wc, kErrWaitFree);
           const uint32_t fb = bar(L::kBarKvFull + slot);
-          mbar_expect_tx(fb, L::kTileBytes);
-          const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
           const int j = i >> 1;
+          if (QK8 && !(i & 1)) {  // int8 K tile: one box of D bytes x 128 rows
+            mbar_expect_tx(fb, kTileN * D);
+            tma_load_4d(sRing + slot * L::kTileBytes, &tm_k, fb, 0, j * kTileN, hk, b);
+          } else {
+            mbar_expect_tx(fb, L::kTileBytes);
+            const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
 #pragma unroll
-          for (int bx = 0; bx < L::kBoxes; ++bx)
-            tma_load_4d(sRing + slot * L::kTileBytes + bx * kBoxBytes, tm, fb, bx * kBoxCols,
-                        j * kTileN, hk, b);
+            for (int bx = 0; bx < L::kBoxes; ++bx)
+              tma_load_4d(sRing + slot * L::kTileBytes + bx * kBoxBytes, tm, fb, bx * kBoxCols,
+                          j * kTileN, hk, b);
+          }
         }
         // On the give-up path copies may still be in flight: let them land (bounded)
         // before the CTA's shared memory is released.
@@ -472,10 +522,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 }
 
 // ---------------------------------------------------------------------------------
-template <int D, bool BF16>
+template <int D, bool BF16, bool QK8>
 static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, cudaStream_t st) {
   using L = WsLayout<D>;
-  auto kern = fwd_ws_kernel<D, BF16>;
+  auto kern = fwd_ws_kernel<D, BF16, QK8>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
   if (e != cudaSuccess) return e;
@@ -490,8 +540,20 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, cudaStre
 cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
                           cudaStream_t st) {
   (void)sm_count;
-  if (D == 128) return bf16 ? launch_ws_t<128, true>(tm, a, st) : launch_ws_t<128, false>(tm, a, st);
-  if (D == 64) return bf16 ? launch_ws_t<64, true>(tm, a, st) : launch_ws_t<64, false>(tm, a, st);
+  if (D == 128)
+    return bf16 ? launch_ws_t<128, true, false>(tm, a, st) : launch_ws_t<128, false, false>(tm, a, st);
+  if (D == 64)
+    return bf16 ? launch_ws_t<64, true, false>(tm, a, st) : launch_ws_t<64, false, false>(tm, a, st);
+  return cudaErrorInvalidValue;
+}
+
+// tm[0], tm[1]: int8 Q / K maps (one box of D bytes x 128 rows); tm[2], tm[3]: 16-bit V / O maps.
+cudaError_t launch_fwd_ws_int8qk(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
+                                 cudaStream_t st) {
+  if (D == 128)
+    return bf16 ? launch_ws_t<128, true, true>(tm, a, st) : launch_ws_t<128, false, true>(tm, a, st);
+  if (D == 64)
+    return bf16 ? launch_ws_t<64, true, true>(tm, a, st) : launch_ws_t<64, false, true>(tm, a, st);
   return cudaErrorInvalidValue;
 }
 

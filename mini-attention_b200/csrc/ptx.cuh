@@ -173,14 +173,15 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 // ---- descriptors --------------------------------------------------------------
 // Shared-memory matrix descriptor (64 bit): start>>4 [0,14), LBO>>4 [16,30),
 // SBO>>4 [32,46), version=1 [46,48), layout type [61,64) (2 = 128-byte swizzle).
+// `layout`: 2 = 128-byte swizzle (default), 4 = 64-byte swizzle, 6 = 32-byte swizzle.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t layout = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= static_cast<uint64_t>(layout) << 61;
   return d;
 }
 

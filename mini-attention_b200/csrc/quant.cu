@@ -1,0 +1,177 @@
+// INT8 pre-pass for the INT8-QK attention variant (no counterpart in the reference code; the
+// recipe is the SageAttention-style one of the task configuration):
+//   1. K is smoothed: the per-(batch, KV head, channel) mean over tokens is subtracted.  Every
+//      score of a row moves by the same amount q.mean(K), so softmax is unchanged.
+//   2. Q and the smoothed K are quantised to int8 with one symmetric fp32 scale per block of 128
+//      tokens: scale = max|x| / 127 over the 128 x D slab (1 for an all-zero slab),
+//      x8 = round-half-even(x / scale), clamped to [-127, 127].
+// Both kernels are HBM-bound byte movers: 16-byte loads, 8-byte int8 stores, grid = one CTA per
+// (128-token block, head, batch).  Algorithmic traffic per element: K 2 B (mean pass) + 2 B + 1 B,
+// Q 2 B + 1 B, plus 4 B per 128 x D slab for the scale.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace ma {
+
+namespace {
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 a;
+    if constexpr (BF16) {
+      a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[i]));
+    } else {
+      a = __half22float2(*reinterpret_cast<const __half2*>(&u[i]));
+    }
+    f[2 * i] = a.x;
+    f[2 * i + 1] = a.y;
+  }
+}
+
+constexpr int kSumRows = 1024;  // tokens per partial column sum
+
+}  // namespace
+
+// partial[b, h, chunk, d] = sum over the chunk's tokens of k[b, h, token, d]
+template <int D, bool BF16>
+__global__ void __launch_bounds__(256)
+k_colsum_kernel(const uint16_t* __restrict__ k, long long sb, long long sh, long long sn, int N,
+                float* __restrict__ partial, int n_chunks) {
+  constexpr int CPR = D / 8;          // 16-byte chunks per row
+  constexpr int RPP = 256 / CPR;      // rows per pass
+  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int col8 = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+  const uint16_t* base = k + b * sb + h * sh;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int row_end = min(N, (chunk + 1) * kSumRows);
+  for (int row = chunk * kSumRows + r0; row < row_end; row += RPP) {
+    const uint4 w = *reinterpret_cast<const uint4*>(base + row * sn + col8 * 8);
+    float f[8];
+    unpack8<BF16>(w, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += f[i];
+  }
+  __shared__ float red[RPP][D];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[r0][col8 * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float s = 0.f;
+#pragma unroll 4
+    for (int r = 0; r < RPP; ++r) s += red[r][threadIdx.x];
+    partial[((static_cast<long long>(b) * gridDim.y + h) * n_chunks + chunk) * D + threadIdx.x] = s;
+  }
+}
+
+// One CTA per (128-token block, head, batch): x8 = round(x' / scale), x' = x - mean (K) or x (Q).
+template <int D, bool BF16, bool SMOOTH>
+__global__ void __launch_bounds__(256)
+quant_block_kernel(const uint16_t* __restrict__ x, long long sb, long long sh, long long sn, int N,
+                   const float* __restrict__ partial, int n_chunks, int8_t* __restrict__ x8,
+                   float* __restrict__ scale_out, float fold, float* __restrict__ mean_out) {
+  constexpr int CPR = D / 8;
+  constexpr int PER = 16 * D / 256;  // chunks per thread (128 rows * D/8 chunks / 256 threads)
+  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int H = gridDim.y, n_blocks = gridDim.x;
+  __shared__ float mean[D];
+  __shared__ float wmax[8];
+  if (SMOOTH) {
+    if (threadIdx.x < D) {
+      float s = 0.f;
+      const float* p = partial + (static_cast<long long>(b) * H + h) * n_chunks * D + threadIdx.x;
+      for (int c = 0; c < n_chunks; ++c) s += p[c * D];
+      const float m = s / static_cast<float>(N);
+      mean[threadIdx.x] = m;
+      if (blk == 0 && mean_out != nullptr) mean_out[(static_cast<long long>(b) * H + h) * D + threadIdx.x] = m;
+    }
+    __syncthreads();
+  }
+  const uint16_t* base = x + b * sb + h * sh;
+  float v[PER][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int id = threadIdx.x + i * 256;
+    const int row = blk * 128 + id / CPR, col8 = id % CPR;
+    if (row < N) {
+      const uint4 w = *reinterpret_cast<const uint4*>(base + row * sn + col8 * 8);
+      unpack8<BF16>(w, v[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (SMOOTH) v[i][e] -= mean[col8 * 8 + e];
+        amax = fmaxf(amax, fabsf(v[i][e]));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = wmax[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, wmax[w]);
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+  if (threadIdx.x == 0)
+    scale_out[(static_cast<long long>(b) * H + h) * n_blocks + blk] = scale * fold;
+  int8_t* obase = x8 + ((static_cast<long long>(b) * H + h) * N) * D;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int id = threadIdx.x + i * 256;
+    const int row = blk * 128 + id / CPR, col8 = id % CPR;
+    if (row < N) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int qv = __float2int_rn(__fdiv_rn(v[i][e], scale));
+        qv = max(-127, min(127, qv));
+        if (e < 4) lo |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * e);
+        else hi |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * (e - 4));
+      }
+      *reinterpret_cast<uint2*>(obase + static_cast<long long>(row) * D + col8 * 8) = make_uint2(lo, hi);
+    }
+  }
+}
+
+// q8/k8: contiguous [B, H, N, D] int8; scales: [B, H, ceil(N/128)] fp32; partial: scratch of
+// B * Hkv * ceil(N/1024) * D floats; k_mean (optional): [B, Hkv, D].
+template <int D, bool BF16>
+static cudaError_t launch_quant_t(const void* q, const long long* qs, const void* k, const long long* ks,
+                                  int B, int Hq, int Hkv, int Nq, int Nk, float q_fold, int8_t* q8,
+                                  int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
+                                  cudaStream_t st) {
+  const int nqb = (Nq + 127) / 128, nkb = (Nk + 127) / 128, nch = (Nk + kSumRows - 1) / kSumRows;
+  if (Nk > 0) {
+    k_colsum_kernel<D, BF16><<<dim3(nch, Hkv, B), 256, 0, st>>>(static_cast<const uint16_t*>(k), ks[0], ks[1],
+                                                               ks[2], Nk, partial, nch);
+    quant_block_kernel<D, BF16, true><<<dim3(nkb, Hkv, B), 256, 0, st>>>(
+        static_cast<const uint16_t*>(k), ks[0], ks[1], ks[2], Nk, partial, nch, k8, sk, 1.0f, k_mean);
+  }
+  if (Nq > 0)
+    quant_block_kernel<D, BF16, false><<<dim3(nqb, Hq, B), 256, 0, st>>>(
+        static_cast<const uint16_t*>(q), qs[0], qs[1], qs[2], Nq, nullptr, 0, q8, sq, q_fold, nullptr);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs, const void* k,
+                            const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk, float q_fold,
+                            int8_t* q8, int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
+                            cudaStream_t st) {
+  if (D == 64)
+    return bf16 ? launch_quant_t<64, true>(q, qs, k, ks, B, Hq, Hkv, Nq, Nk, q_fold, q8, k8, sq, sk, partial, k_mean, st)
+                : launch_quant_t<64, false>(q, qs, k, ks, B, Hq, Hkv, Nq, Nk, q_fold, q8, k8, sq, sk, partial, k_mean, st);
+  if (D == 128)
+    return bf16 ? launch_quant_t<128, true>(q, qs, k, ks, B, Hq, Hkv, Nq, Nk, q_fold, q8, k8, sq, sk, partial, k_mean, st)
+                : launch_quant_t<128, false>(q, qs, k, ks, B, Hq, Hkv, Nq, Nk, q_fold, q8, k8, sq, sk, partial, k_mean, st);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace ma

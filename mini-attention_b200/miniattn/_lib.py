@@ -32,6 +32,15 @@ class FwdParams(C.Structure):
     ]
 
 
+class Int8Params(C.Structure):
+    """Mirror of ``MiniAttnInt8Params``."""
+
+    _fields_ = [
+        ("fwd", FwdParams), ("q8", C.c_void_p), ("k8", C.c_void_p), ("q_scale", C.c_void_p),
+        ("k_scale", C.c_void_p), ("k_partial", C.c_void_p), ("k_mean", C.c_void_p),
+    ]
+
+
 class MergeParams(C.Structure):
     """Mirror of ``MiniAttnMergeParams``."""
 
@@ -51,6 +60,9 @@ def _load() -> C.CDLL:
     lib = C.CDLL(str(_LIB_PATH))
     lib.miniattn_fwd.argtypes = [C.POINTER(FwdParams), C.c_void_p]
     lib.miniattn_fwd.restype = C.c_int
+    for name in ("miniattn_quant_qk_int8", "miniattn_fwd_int8qk"):
+        getattr(lib, name).argtypes = [C.POINTER(Int8Params), C.c_void_p]
+        getattr(lib, name).restype = C.c_int
     lib.miniattn_merge_partials.argtypes = [C.POINTER(MergeParams), C.c_void_p]
     lib.miniattn_merge_partials.restype = C.c_int
     lib.miniattn_selftest_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]

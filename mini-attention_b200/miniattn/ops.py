@@ -54,30 +54,9 @@ def _bhnd_shape(t: torch.Tensor, layout: str) -> Tuple[int, int, int, int]:
     return b, h, n, d
 
 
-def flash_attn_fwd(
-    q: torch.Tensor,
-    k: torch.Tensor,
-    v: torch.Tensor,
-    *,
-    causal: bool = False,
-    softmax_scale: Optional[float] = None,
-    layout: str = "bhnd",
-    return_lse: bool = False,
-    out: Optional[torch.Tensor] = None,
-    kernel: str = "auto",
-    q_pos0: int = 0,
-    k_pos0: int = 0,
-):
-    """O = softmax(Q K^T * scale [+ causal mask]) V on the GPU.
-
-    q: (B,Hq,Nq,D) for ``layout="bhnd"`` or (B,Nq,Hq,D) for ``"bnhd"`` (the layout of the
-    reference CUDA operator, flash_attention.cu:68-70); k, v likewise with Hkv heads where
-    Hkv divides Hq (KV head g serves query heads g*G..g*G+G-1, as
-    kernels/standard/pytorch/gqa.py:38-39).  Causal: key j is visible to query i iff
-    ``k_pos0 + j <= q_pos0 + i`` (kernels/flash_attn/triton/fp16_flash_attn_sm86.py:74-75
-    with both offsets 0).  Returns ``out`` or ``(out, lse)`` with lse fp32 (B,Hq,Nq) =
-    natural-log of the softmax denominator.
-    """
+def _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0):
+    """Validate like the reference launcher and fill a FwdParams block.  Returns
+    (params or None when the problem is empty, out, lse)."""
     if layout not in ("bhnd", "bnhd"):
         raise RuntimeError(f"layout must be 'bhnd' or 'bnhd', got {layout!r}")
     if kernel not in _lib.KERNELS:
@@ -112,8 +91,7 @@ def flash_attn_fwd(
             raise RuntimeError("out must be contiguous in the head dimension")
     lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device) if return_lse else None
     if q.numel() == 0:
-        return (out, lse) if return_lse else out
-
+        return None, out, lse
     p = _lib.FwdParams()
     p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
     p.lse = lse.data_ptr() if lse is not None else None
@@ -128,10 +106,98 @@ def flash_attn_fwd(
     p.causal = 1 if causal else 0
     p.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
     p.kernel = _lib.KERNELS[kernel]
+    return p, out, lse
+
+
+def flash_attn_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+    layout: str = "bhnd",
+    return_lse: bool = False,
+    out: Optional[torch.Tensor] = None,
+    kernel: str = "auto",
+    q_pos0: int = 0,
+    k_pos0: int = 0,
+):
+    """O = softmax(Q K^T * scale [+ causal mask]) V on the GPU.
+
+    q: (B,Hq,Nq,D) for ``layout="bhnd"`` or (B,Nq,Hq,D) for ``"bnhd"`` (the layout of the
+    reference CUDA operator, flash_attention.cu:68-70); k, v likewise with Hkv heads where
+    Hkv divides Hq (KV head g serves query heads g*G..g*G+G-1, as
+    kernels/standard/pytorch/gqa.py:38-39).  Causal: key j is visible to query i iff
+    ``k_pos0 + j <= q_pos0 + i`` (kernels/flash_attn/triton/fp16_flash_attn_sm86.py:74-75
+    with both offsets 0).  Returns ``out`` or ``(out, lse)`` with lse fp32 (B,Hq,Nq) =
+    natural-log of the softmax denominator.
+    """
+    p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0)
+    if p is not None:
+        with torch.cuda.device(q.device):
+            stream = torch.cuda.current_stream(q.device).cuda_stream
+            rc = _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
+        _lib.check(rc, "miniattn_fwd")
+    return (out, lse) if return_lse else out
+
+
+class Int8QK:
+    """Device buffers of the INT8-QK pre-pass for one problem shape: int8 Q and K, their
+    per-128-token-block scales, the K channel means and the column-sum scratch."""
+
+    def __init__(self, B, Hq, Hkv, Nq, Nk, D, device):
+        nqb, nkb, nch = (Nq + 127) // 128, (Nk + 127) // 128, (Nk + 1023) // 1024
+        self.shape = (B, Hq, Hkv, Nq, Nk, D)
+        self.q8 = torch.empty((B, Hq, Nq, D), dtype=torch.int8, device=device)
+        self.k8 = torch.empty((B, Hkv, Nk, D), dtype=torch.int8, device=device)
+        self.q_scale = torch.empty((B, Hq, nqb), dtype=torch.float32, device=device)
+        self.k_scale = torch.empty((B, Hkv, nkb), dtype=torch.float32, device=device)
+        self.k_partial = torch.empty((B, Hkv, nch, D), dtype=torch.float32, device=device)
+        self.k_mean = torch.empty((B, Hkv, D), dtype=torch.float32, device=device)
+
+    def fill(self, p8: "_lib.Int8Params") -> None:
+        p8.q8, p8.k8 = self.q8.data_ptr(), self.k8.data_ptr()
+        p8.q_scale, p8.k_scale = self.q_scale.data_ptr(), self.k_scale.data_ptr()
+        p8.k_partial, p8.k_mean = self.k_partial.data_ptr(), self.k_mean.data_ptr()
+
+
+def flash_attn_fwd_int8qk(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+    layout: str = "bhnd",
+    return_lse: bool = False,
+    out: Optional[torch.Tensor] = None,
+    buffers: Optional[Int8QK] = None,
+    quantize: bool = True,
+    attend: bool = True,
+):
+    """INT8-QK attention: K is mean-smoothed, Q and K are quantised to int8 per block of 128
+    tokens (pre-pass), Q8 K8^T runs on the int8 tensor cores, P V stays 16 bit.  `buffers` lets a
+    caller reuse the pre-pass buffers across calls of the same shape (and inspect them);
+    ``quantize=False`` skips the pre-pass (buffers already filled), ``attend=False`` runs the
+    pre-pass only."""
+    p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, "auto", 0, 0)
+    if p is None:
+        return (out, lse) if return_lse else out
+    shape = (p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D)
+    if buffers is None:
+        buffers = Int8QK(*shape, q.device)
+    elif buffers.shape != shape or buffers.q8.device != q.device:
+        raise RuntimeError("buffers were made for another problem shape or device")
+    p8 = _lib.Int8Params()
+    p8.fwd = p
+    buffers.fill(p8)
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream(q.device).cuda_stream
-        rc = _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
-    _lib.check(rc, "miniattn_fwd")
+        if quantize:
+            _lib.check(_lib.lib.miniattn_quant_qk_int8(C.byref(p8), C.c_void_p(stream)), "miniattn_quant_qk_int8")
+        if attend:
+            _lib.check(_lib.lib.miniattn_fwd_int8qk(C.byref(p8), C.c_void_p(stream)), "miniattn_fwd_int8qk")
     return (out, lse) if return_lse else out
 
 

@@ -1,0 +1,84 @@
+"""INT8-QK variant: the quantisation pre-pass against the oracle's quantiser, and the attention
+result against (a) the oracle's restatement of the INT8 recipe and (b) the fp16 reference with the
+north-star bar cosine similarity >= 0.999.  The reference repository holds no INT8 code, so these
+sub-paths are pinned by the recipe stated in the task configuration only."""
+import math
+
+import pytest
+import torch
+
+import miniattn
+from oracle.attention_oracle import attention_reference, int8qk_reference, make_inputs, quantize_per_block_int8
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def config4_inputs(B, H, N, D, dtype=torch.float16, seed=0, hkv=None):
+    """q, k, v ~ N(0,1); k gets a per-channel offset ~ N(0, 2) shared by all tokens."""
+    hkv = H if hkv is None else hkv
+    q, k, v = make_inputs(B, H, hkv, N, N, D, dtype, seed)
+    off = 2.0 * torch.randn(1, 1, 1, D, generator=torch.Generator().manual_seed(seed + 1))
+    return q, (k.float() + off).to(dtype), v
+
+
+def cosine(a, b):
+    a, b = a.float().flatten(), b.float().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D,N", [(64, 512), (128, 300), (64, 1100)])
+def test_quant_prepass_matches_oracle(dtype, D, N):
+    q, k, v = config4_inputs(2, 4, N, D, dtype, seed=N, hkv=2)
+    buf = miniattn.Int8QK(2, 4, 2, N, N, D, DEV)
+    miniattn.flash_attn_fwd_int8qk(q.to(DEV), k.to(DEV), v.to(DEV), buffers=buf, attend=False)
+    q8_ref, sq_ref = quantize_per_block_int8(q.float())
+    mean_ref = k.float().mean(dim=2)
+    k8_ref, sk_ref = quantize_per_block_int8(k.float() - mean_ref.unsqueeze(2))
+    fold = (1.0 / math.sqrt(D)) * 1.4426950408889634
+    # Q: same arithmetic, bit-exact
+    assert torch.equal(buf.q8.cpu(), q8_ref)
+    assert torch.allclose(buf.q_scale.cpu(), sq_ref * fold, rtol=1e-6, atol=0)
+    # K: the channel mean is summed in a different order than torch's, so allow the last bit of
+    # the mean to differ: scales agree to 1e-5 and at most a few elements land on the other side
+    # of a rounding boundary, by one step
+    assert (buf.k_mean.cpu() - mean_ref).abs().max().item() < 1e-5
+    assert torch.allclose(buf.k_scale.cpu(), sk_ref, rtol=1e-5, atol=0)
+    diff = (buf.k8.cpu().int() - k8_ref.int()).abs()
+    assert diff.max().item() <= 1 and (diff > 0).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype,D,Hq,Hkv,N", [
+    (torch.float16, 64, 4, 4, 1024),
+    (torch.float16, 128, 4, 2, 640),
+    (torch.bfloat16, 64, 2, 1, 333),
+])
+def test_int8qk_attention(causal, dtype, D, Hq, Hkv, N):
+    q, k, v = config4_inputs(1, Hq, N, D, dtype, seed=D + N, hkv=Hkv)
+    out, lse = miniattn.flash_attn_fwd_int8qk(q.to(DEV), k.to(DEV), v.to(DEV), causal=causal, return_lse=True)
+    assert miniattn.device_status(DEV) == 0
+    out = out.cpu()
+    ref8 = int8qk_reference(q, k, v, causal=causal)
+    ref = attention_reference(q, k, v, causal=causal, out_dtype=torch.float32)
+    # against the same recipe on the CPU: only rounding-boundary flips of K and accumulation order differ
+    assert (out.float() - ref8.float()).abs().max().item() <= (4e-3 if dtype == torch.float16 else 2e-2)
+    # north-star bar against the un-quantised reference
+    assert cosine(out, ref) >= 0.999
+    assert torch.isfinite(lse).all()
+
+
+def test_config4_full_size():
+    """B=2 H=16 N=8192 D=64 fp16, K with a per-channel offset: cosine >= 0.999 vs the fp16-input
+    reference on sampled rows (exact fp32 oracle), and the smoothing must matter: without it the
+    same quantiser does visibly worse."""
+    from oracle.attention_oracle import attention_reference_rows
+    q, k, v = config4_inputs(2, 16, 8192, 64, torch.float16, seed=0)
+    out = miniattn.flash_attn_fwd_int8qk(q.to(DEV), k.to(DEV), v.to(DEV)).cpu()
+    assert miniattn.device_status(DEV) == 0
+    rows = torch.randint(0, 8192, (96,), generator=torch.Generator().manual_seed(4)).unique()
+    ref = attention_reference_rows(q, k, v, rows)
+    assert cosine(out[:, :, rows], ref) >= 0.999
+    fp16 = miniattn.flash_attn_fwd(q.to(DEV), k.to(DEV), v.to(DEV)).cpu()
+    assert cosine(out, fp16) >= 0.999
