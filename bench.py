@@ -10,6 +10,9 @@ Workloads (``--workload``):
                 B=2 shard of a batch of 2*N (sharded by batch x head, no communication): weak scaling.
   c3            GQA causal bf16 B=4 Hq=32 Hkv=8 N=4096 D=128, the (batch x KV-head) groups split
                 across the ranks, no communication: strong scaling.
+  c4            SageAttention-style INT8-QK forward, B=2 H=16 N=8192 D=64: the step is the pre-pass
+                (K mean-smoothing + int8 quantisation of Q and K) plus the attention kernel; the
+                attention kernel alone is reported under ``attention_only``.
   c5            causal MHA fp16 B=1 H=32 N=131072 D=128 in ring / context-parallel mode: zig-zag
                 sequence split, K/V pairs travel over NCCL send/recv while the resident Q blocks
                 attend to the visiting pair, log-sum-exp merge of the partials: strong scaling.
@@ -46,6 +49,9 @@ WORKLOADS = {
                name="MHA fwd non-causal fp16 B=2 H=8 N=8192 D=128 (top of the N=512..8192 sweep)"),
     "c3": dict(B=4, Hq=32, Hkv=8, N=4096, D=128, dtype="bf16", causal=True,
                name="GQA fwd causal bf16 B=4 Hq=32 Hkv=8 N=4096 D=128, (batch x KV-head) groups sharded"),
+    "c4": dict(B=2, Hq=16, Hkv=16, N=8192, D=64, dtype="fp16", causal=False, int8qk=True,
+               name="INT8-QK fwd non-causal B=2 H=16 N=8192 D=64 (fp16 in, K offset N(0,2) per channel, "
+                    "int8 Q/K per 128-token block, fp16 PV); pre-pass inside the step"),
     "c5": dict(B=1, Hq=32, Hkv=32, N=131072, D=128, dtype="fp16", causal=True,
                name="long-context causal MHA fwd fp16 B=1 H=32 N=131072 D=128, zig-zag ring over the GPUs"),
 }
@@ -256,7 +262,16 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
     launches_per_step = 1
-    if ring:
+    int8 = bool(w.get("int8qk"))
+    if int8:
+        hk.copy_((hk.float() + 2.0 * torch.randn(1, 1, 1, D, generator=g)).to(dt))  # per-channel K offset
+        k.copy_(hk)
+        bufs = miniattn.Int8QK(sB, sHq, sHkv, sN, sN, D, dev)
+        launches_per_step = 4  # column sums, K quantiser, Q quantiser, attention
+
+        def attend():
+            miniattn.flash_attn_fwd_int8qk(q, k, v, causal=causal, out=o, buffers=bufs)
+    elif ring:
         from miniattn import parallel as par
         n_tasks = sum(len(par.ring_step_tasks(rank, world, s_, causal)) for s_ in range(world))
         launches_per_step = 2 * n_tasks  # one attention + one merge launch per task
@@ -309,6 +324,18 @@ def main():
     ms_e2e = ms_dev if args.no_e2e else timed(step_e2e, max(3, args.steps // 2), 3)
     status = miniattn.device_status(dev)
 
+    extra = {}
+    if int8:
+        def attn_only():
+            miniattn.flash_attn_fwd_int8qk(q, k, v, causal=causal, out=o, buffers=bufs, quantize=False)
+
+        def prepass_only():
+            miniattn.flash_attn_fwd_int8qk(q, k, v, causal=causal, out=o, buffers=bufs, attend=False)
+        ms_a = timed(attn_only, args.steps, 3)
+        ms_p = timed(prepass_only, args.steps, 3)
+        pre_bytes = (sHq + 2 * sHkv) * sB * sN * D * 2 + (sHq + sHkv) * sB * sN * D
+        extra["attention_only"] = {"ms": ms_a, "tflops": step_flops / ms_a / 1e9}
+        extra["prepass_only"] = {"ms": ms_p, "algorithmic_bytes": pre_bytes, "hbm_gbs": pre_bytes / ms_p / 1e6}
     sweep = {}
     if args.workload == "c2" and rank == 0 and not args.no_sweep:
         for n in SWEEP_N:
@@ -360,6 +387,7 @@ def main():
         }
         if sweep:
             line["sweep"] = sweep
+        line.update(extra)
         if world == 1 and not args.no_cpu_baseline:
             tf, cores, desc = cpu_attention_sample(w, 20.0)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": desc}
