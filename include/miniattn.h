@@ -110,6 +110,31 @@ int miniattn_quant_qk_int8(const MiniAttnInt8Params* p, void* stream);
 int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream);
 
 /*
+ * Allocation-free form of the INT8 pre-pass.  It has no counterpart in the reference.
+ *
+ * Who needs it: hosts that give this library no way to get device memory of its own — a serving
+ * runtime that reserved the whole GPU for its KV cache at start-up, or a plugin slot whose
+ * contract forbids cudaMalloc because an allocation synchronises the device and can fail long
+ * after start-up.  Such a caller owns q, k and the outputs (q8, k8, q_scale, k_scale, optional
+ * k_mean) but has nowhere to put the pre-pass's internal scratch, the per-1024-token column sums
+ * of K.  This entry point keeps that scratch in a fixed array inside the library instead:
+ * p->k_partial is ignored (it may be NULL) and neither this call nor anything it runs calls
+ * cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * Limit: B * Hkv * ceil(Nk/1024) * D <= 65536 floats (256 KB, held by every GPU that loads the
+ * library until the process exits); larger problems are refused with MINIATTN_EUNSUPPORTED and a
+ * message naming both numbers.  Results are identical to miniattn_quant_qk_int8.
+ *
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call outside any stream capture.  All calls on a device share the one array,
+ * which keeps whatever the last call left in it: nothing in it needs clearing (every entry that is
+ * read is written earlier in the same call), but two calls whose kernels overlap on the GPU —
+ * different streams, no ordering between them — race on it.  Keep such calls on one stream or
+ * order them with events.
+ */
+int miniattn_quant_qk_int8_static(const MiniAttnInt8Params* p, void* stream);
+
+/*
  * Log-sum-exp merge of attention partials, used by the ring (context-parallel) launcher.
  * No reference counterpart on the CUDA side; the arithmetic is the split-KV merge of
  * kernels/standard/pytorch/benchmark_mla_decode_torch.py:244-272 applied to two partials:

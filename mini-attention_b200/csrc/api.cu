@@ -25,6 +25,11 @@ cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs
                             const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk, float q_fold,
                             int8_t* q8, int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
                             cudaStream_t st);
+long long static_colsum_capacity();
+cudaError_t launch_quant_qk_static(int D, bool bf16, const void* q, const long long* qs, const void* k,
+                                   const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk,
+                                   float q_fold, int8_t* q8, int8_t* k8, float* sq, float* sk,
+                                   float* k_mean, cudaStream_t st);
 cudaError_t launch_wait_selftest(int32_t* status, unsigned long long limit_ns, cudaStream_t st);
 cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part_o,
                                   const float* part_lse, void* out, long long rows, int D, bool bf16,
@@ -276,6 +281,31 @@ int miniattn_quant_qk_int8(const MiniAttnInt8Params* p, void* stream) {
                                       reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return MINIATTN_OK;
+}
+
+int miniattn_quant_qk_int8_static(const MiniAttnInt8Params* p, void* stream) {
+  g_err[0] = 0;
+  int rc = check_int8_params(p, false);
+  if (rc != 0) return rc > 0 ? MINIATTN_OK : rc;
+  int sms = 0;
+  if ((rc = check_device(&sms)) != 0) return rc;
+  const MiniAttnFwdParams& f = p->fwd;
+  const long long need = (long long)f.B * f.Hkv * ((f.Nk + 1023) / 1024) * f.D;
+  if (need > ma::static_colsum_capacity())
+    return fail(MINIATTN_EUNSUPPORTED,
+                "B*Hkv*ceil(Nk/1024)*D = %lld floats of column-sum scratch exceed the built-in %lld; "
+                "use miniattn_quant_qk_int8 with a caller-provided k_partial buffer",
+                need, ma::static_colsum_capacity());
+  const float scale = f.softmax_scale > 0.f ? f.softmax_scale : 1.0f / sqrtf((float)f.D);
+  const long long qs[3] = {f.q_stride[0], f.q_stride[1], f.q_stride[2]};
+  const long long ks[3] = {f.k_stride[0], f.k_stride[1], f.k_stride[2]};
+  cudaError_t e = ma::launch_quant_qk_static(f.D, f.dtype == MINIATTN_BF16, f.q, qs, f.k, ks, f.B, f.Hq,
+                                             f.Hkv, f.Nq, f.Nk, scale * 1.4426950408889634f, p->q8, p->k8,
+                                             p->q_scale, p->k_scale, p->k_mean,
+                                             reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess)
+    return fail(MINIATTN_ECUDA, "pre-pass set-up or launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;
 }
 

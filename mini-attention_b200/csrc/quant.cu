@@ -13,8 +13,16 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <mutex>
 
 namespace ma {
+
+// Scratch of the allocation-free pre-pass entry point (miniattn_quant_qk_int8_static): the
+// column sums of K, B * Hkv * ceil(Nk/1024) * D floats, at most kStaticColsumFloats (256 KB).
+// Every GPU that loads the library holds this array until the process exits.  In host code the
+// name below is only a handle for cudaGetSymbolAddress, never a device address.
+constexpr long long kStaticColsumFloats = 65536;
+static __device__ __align__(256) float g_static_colsum[kStaticColsumFloats];
 
 namespace {
 
@@ -172,6 +180,42 @@ cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs
     return bf16 ? launch_quant_t<128, true>(q, qs, k, ks, B, Hq, Hkv, Nq, Nk, q_fold, q8, k8, sq, sk, partial, k_mean, st)
                 : launch_quant_t<128, false>(q, qs, k, ks, B, Hq, Hkv, Nq, Nk, q_fold, q8, k8, sq, sk, partial, k_mean, st);
   return cudaErrorInvalidValue;
+}
+
+long long static_colsum_capacity() { return kStaticColsumFloats; }
+
+// Device address of g_static_colsum on the current device, looked up once per device with that
+// device current (the first call on a device does the lookup).
+static cudaError_t static_colsum_ptr(float** out) {
+  static std::mutex mu;
+  static float* ptrs[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_colsum);
+    if (e != cudaSuccess) return e;
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return cudaSuccess;
+}
+
+// Same pre-pass as launch_quant_qk with the column-sum scratch taken from g_static_colsum.
+// Nothing in the array has to start at zero: the column-sum kernel overwrites every entry the
+// quantiser reads.  The caller has checked that the problem fits kStaticColsumFloats.
+cudaError_t launch_quant_qk_static(int D, bool bf16, const void* q, const long long* qs, const void* k,
+                                   const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk,
+                                   float q_fold, int8_t* q8, int8_t* k8, float* sq, float* sk,
+                                   float* k_mean, cudaStream_t st) {
+  float* scratch = nullptr;
+  cudaError_t e = static_colsum_ptr(&scratch);
+  if (e != cudaSuccess) return e;
+  return launch_quant_qk(D, bf16, q, qs, k, ks, B, Hq, Hkv, Nq, Nk, q_fold, q8, k8, sq, sk, scratch,
+                         k_mean, st);
 }
 
 }  // namespace ma

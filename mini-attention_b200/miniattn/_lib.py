@@ -60,7 +60,7 @@ def _load() -> C.CDLL:
     lib = C.CDLL(str(_LIB_PATH))
     lib.miniattn_fwd.argtypes = [C.POINTER(FwdParams), C.c_void_p]
     lib.miniattn_fwd.restype = C.c_int
-    for name in ("miniattn_quant_qk_int8", "miniattn_fwd_int8qk"):
+    for name in ("miniattn_quant_qk_int8", "miniattn_quant_qk_int8_static", "miniattn_fwd_int8qk"):
         getattr(lib, name).argtypes = [C.POINTER(Int8Params), C.c_void_p]
         getattr(lib, name).restype = C.c_int
     lib.miniattn_merge_partials.argtypes = [C.POINTER(MergeParams), C.c_void_p]
