@@ -191,6 +191,39 @@ def run_reference_arm(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def reference_gpu_kernel_leg(B, H, N_list, D, dev, flush, stream):
+    """Optional baseline: the reference's own mma.sync kernel (newest tree, K7 config) rebuilt for
+    sm_100 by oracle/build_ref_kernel.py, timed on this GPU with the same protocol.  Returns {} when
+    the built extension is not present."""
+    try:
+        from oracle.build_ref_kernel import load_built
+        ext = load_built()
+    except Exception as e:  # missing file, ABI mismatch ...
+        return {"unavailable": repr(e)}
+    if ext is None:
+        return {}
+    from miniattn.kernel_configs import get_kernel_progression_configs
+    cfg = get_kernel_progression_configs()[6]
+    out = {"kernel": "reference flash_forward_kernel (mma.sync), K7 config, rebuilt for sm_100"}
+    for n in N_list:
+        q = torch.randn(B, n, H, D, device=dev, dtype=torch.float16)  # the reference's (B,N,H,D) layout
+        k, v = torch.randn_like(q), torch.randn_like(q)
+        o = torch.empty_like(q)
+        for _ in range(3):
+            ext.forward(cfg, q, k, v, o, False)
+        torch.cuda.synchronize(dev)
+        tot = 0.0
+        for _ in range(10):
+            flush.zero_()
+            torch.cuda.synchronize(dev)
+            # benchmark=True: the extension brackets its own launch with CUDA events
+            # (flash_attention.cu:111-131); its Python-side call overhead stays outside
+            _, ms = ext.forward(cfg, q, k, v, o, True)
+            tot += ms
+        out[str(n)] = {"ms": tot / 10, "tflops": flops(B, H, n, D, False) / (tot / 10) / 1e9}
+    return out
+
+
 # ------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -354,6 +387,10 @@ def main():
                 b_.synchronize()
                 tot += a.elapsed_time(b_)
             sweep[str(n)] = {"ms": tot / 10, "tflops": flops(B, Hq, n, D, False) / (tot / 10) / 1e9}
+    if args.workload == "c2" and rank == 0 and not args.no_sweep and world == 1:
+        ref_leg = reference_gpu_kernel_leg(B, Hq, SWEEP_N + (N,), D, dev, flush, stream)
+        if ref_leg:
+            extra["reference_kernel_on_this_gpu"] = ref_leg
     if world > 1:
         dist.barrier()
 

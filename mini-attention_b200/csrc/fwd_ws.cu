@@ -1,29 +1,33 @@
 // Forward attention, warp-specialised sm_100a kernel.
 //
-// One CTA (512 threads) per work item = two 128-row Q tiles of one (batch, head).  The two
-// tiles are ping-ponged so that the exp2 / online-softmax work of one overlaps the
-// tensor-core work of the other.  Same math as the reference mainloop
-// (kernels/flash_attn/cuda/sm_120/kernel/include/forward_kernel.cuh:137-221 and
-// softmax.cuh:29-138), restructured for tcgen05 / TMEM / TMA:
+// One CTA (512 threads) per work item = two 128-row Q tiles of one (batch, head).  Same math as
+// the reference mainloop (kernels/flash_attn/cuda/sm_120/kernel/include/forward_kernel.cuh:137-221
+// and softmax.cuh:29-138), restructured for tcgen05 / TMEM / TMA:
 //
 //   warps 0-3   softmax of Q tile 0   (thread = one query row; S row read from TMEM)
 //   warps 4-7   softmax of Q tile 1
 //   warps 8-11  correction: rescales the O accumulators in TMEM when a row maximum moved,
 //               and runs the epilogue (O / l -> 16 bit -> swizzled smem -> TMA store)
-//   warp 12     MMA issuer: one thread issues every tcgen05.mma
+//   warp 12     MMA issuer of Q tile 0 (one thread issues its tcgen05.mma stream)
+//   warp 14     MMA issuer of Q tile 1
 //   warp 13     TMA producer: Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring
-//   warps 14-15 idle (they donate their registers)
+//   warp 15     idle (donates its registers)
 //
-// TMEM (512 columns x 128 lanes x 32 bit): S0 [0,128)  S1 [128,256)  O0 [256,256+D)
-// O1 [256+D,256+2D).  P (16 bit) overwrites the first 64 columns of its S tile and is fed to
-// the PV MMA straight from TMEM (A operand), so P never touches shared memory.
+// A 128-key K/V tile is worked on as two 64-key halves ("a", "b").  Each Q tile owns two S
+// buffers of 64 TMEM columns; the 16-bit P of a half overwrites the first 32 columns of its own
+// S buffer and feeds the PV MMA straight from TMEM (A operand).  Because the halves have separate
+// buffers, S_half(j+1) is computed while the softmax group still works on the other half, so the
+// softmax never waits for the chain  P -> PV -> next S  of the half it just finished.
 //
-// Tensor-pipe order per K/V tile j:  PV0(j)  S0(j+1)  PV1(j)  S1(j+1).
+// TMEM (512 columns x 128 lanes x 32 bit):
+//   S0a [0,64) S0b [64,128) S1a [128,192) S1b [192,256)   O0 [256,256+D)  O1 [256+D,256+2D)
 //
-// The row maximum is updated lazily: a row keeps exponentiating against a stale maximum
-// until the true maximum has grown by more than 2^8 (in the exp2 domain), so the O
-// accumulator is rescaled only rarely; l is accumulated against the same maximum, which
-// keeps O / l exact.
+// MMA order per Q tile and K/V tile j:  PV_a(j) S_a(j+1) PV_b(j) S_b(j+1); the two tiles have
+// one issuing thread each and the tensor pipe interleaves their streams.
+//
+// The row maximum is updated lazily: a row keeps exponentiating against a stale maximum until the
+// true maximum has grown by more than 2^8 (in the exp2 domain), so the O accumulator is rescaled
+// only rarely; l is accumulated against the same maximum, which keeps O / l exact.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -32,14 +36,15 @@ namespace ma {
 namespace {
 
 constexpr int kNumThreads = 512;
-// Register split per thread after setmaxnreg (8 softmax + 4 correction + 4 other warps;
-// 8*168 + 4*96 + 4*80 = 2048 = the 64 K registers of an SM divided by 32 lanes).
-#ifndef MA_REG_SOFTMAX
-#define MA_REG_SOFTMAX 168
-#define MA_REG_CORR 96
-#define MA_REG_OTHER 80
-#endif
+constexpr int kHalfN = kTileN / 2;      // keys per half tile
 constexpr float kLazyThreshold = 8.0f;  // log2 units
+// Register split per thread after setmaxnreg (8 softmax + 4 correction + 4 other warps;
+// 8*176 + 4*88 + 4*72 = 2048 = the 64 K registers of an SM divided by 32 lanes).
+#ifndef MA_REG_SOFTMAX
+#define MA_REG_SOFTMAX 176
+#define MA_REG_CORR 88
+#define MA_REG_OTHER 72
+#endif
 
 template <int D>
 struct WsLayout {
@@ -48,25 +53,26 @@ struct WsLayout {
   static constexpr int kStages = (D == 128) ? 4 : 8;     // ring slots, each one K or V tile
   static constexpr int kOffQ = 0;                        // two Q tiles (reused as O staging)
   static constexpr int kOffRing = 2 * kTileBytes;
-  static constexpr int kOffAlpha = kOffRing + kStages * kTileBytes;  // float[2][128]
-  static constexpr int kOffL = kOffAlpha + 1024;                     // float[2][128]
+  static constexpr int kOffAlpha = kOffRing + kStages * kTileBytes;  // float[2 tiles][2 halves][128]
+  static constexpr int kOffL = kOffAlpha + 2048;                     // float[2][128]
   static constexpr int kOffBar = kOffL + 1024;
-  // barrier indices (8 bytes each)
+  // barrier indices (8 bytes each); [t][h] = index + 2*t + h
   static constexpr int kBarQFull = 0;                      // [2]
   static constexpr int kBarKvFull = 2;                     // [kStages]
   static constexpr int kBarKvEmpty = kBarKvFull + kStages; // [kStages]
-  static constexpr int kBarSFull = kBarKvEmpty + kStages;  // [2]  MMA -> softmax
-  static constexpr int kBarPReady = kBarSFull + 2;         // [2][2] softmax -> MMA, per half of P
-  static constexpr int kBarAlpha = kBarPReady + 4;         // [2]  softmax -> correction
-  static constexpr int kBarOReady = kBarAlpha + 2;         // [2]  correction -> MMA
-  static constexpr int kBarODone = kBarOReady + 2;         // [2]  MMA -> correction
-  static constexpr int kBarLReady = kBarODone + 2;         // [2]  softmax -> correction (final l)
+  static constexpr int kBarSFull = kBarKvEmpty + kStages;  // [2][2] MMA -> softmax
+  static constexpr int kBarPReady = kBarSFull + 4;         // [2][2] softmax -> MMA
+  static constexpr int kBarAlpha = kBarPReady + 4;         // [2][2] softmax -> correction
+  static constexpr int kBarOReady = kBarAlpha + 4;         // [2][2] correction -> MMA
+  static constexpr int kBarODone = kBarOReady + 4;         // [2][2] MMA -> correction
+  static constexpr int kBarLReady = kBarODone + 4;         // [2]    softmax -> correction (final l)
   static constexpr int kNumBars = kBarLReady + 2;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem slot, abort flag
   static constexpr int kBytes = kOffMisc + 16;
   static constexpr int kDynSmem = kBytes + 1024;
   static constexpr int kTmemCols = 512;
-  static constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
+  static constexpr int kColS = 0;     // S buffer of (tile t, half h) at kColS + 128*t + 64*h
+  static constexpr int kColO = 256;   // O accumulator of tile t at kColO + D*t
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
@@ -150,17 +156,17 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(bar(L::kBarQFull + 1), 1);
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(bar(L::kBarKvFull + s), 1);
-      mbar_init(bar(L::kBarKvEmpty + s), 1);
+      mbar_init(bar(L::kBarKvEmpty + s), nt);  // one release per issuing thread
     }
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(bar(L::kBarSFull + t), 1);
-      mbar_init(bar(L::kBarPReady + 2 * t), 4);
-      mbar_init(bar(L::kBarPReady + 2 * t + 1), 4);
-      mbar_init(bar(L::kBarAlpha + t), 4);
-      mbar_init(bar(L::kBarOReady + t), 4);
-      mbar_init(bar(L::kBarODone + t), 1);
-      mbar_init(bar(L::kBarLReady + t), 4);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar(L::kBarSFull + i), 1);
+      mbar_init(bar(L::kBarPReady + i), 4);
+      mbar_init(bar(L::kBarAlpha + i), 4);
+      mbar_init(bar(L::kBarOReady + i), 4);
+      mbar_init(bar(L::kBarODone + i), 1);
     }
+    mbar_init(bar(L::kBarLReady + 0), 4);
+    mbar_init(bar(L::kBarLReady + 1), 4);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_q);
@@ -190,7 +196,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const int r = tid & 127;
       const int row = q0 + t * kTileM + r;
       const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      const uint32_t tS = tmem_base + (t ? L::kColS1 : L::kColS0) + lane_off;
+      const uint32_t tS = tmem_base + L::kColS + 128 * t + lane_off;
       long long vis_ll = a.Nk;
       if (a.causal) vis_ll = min(vis_ll, a.q_pos0 + row - a.k_pos0 + 1);
       const int vis_row = static_cast<int>(max(0ll, vis_ll));
@@ -205,90 +211,86 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
 
       for (int j = 0; j < n_tiles; ++j) {
-        mbar_wait(bar(L::kBarSFull + t), j & 1, wc, kErrWaitS);
-        tc_fence_after();
-        if (r == 0) MA_STAMP(t, 1);
-        uint32_t s[4][32];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) tmem_ld32(tS + q * 32, s[q]);
-        tmem_wait_ld();
-        if (r == 0) MA_STAMP(t, 2);
-
         // cj turns a raw score into log2 units: softmax scale * log2e, times the two
         // de-quantisation scales of this (Q block, K block) for the int8 variant.
         float cj = c;
         if constexpr (QK8) {
           cj = sq_t * sk_next;
           if (j + 1 < n_tiles) sk_next = __ldg(sk_row + j + 1);
-          // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding the
-          // bit pattern of 1.5*2^23 and subtracting that value is exact.
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              s[q][i] = __float_as_uint(__uint_as_float(s[q][i] + 0x4B400000u) - 12582912.f);
         }
-        const int lim = vis_row - j * kTileN;
-        if (lim < kTileN) {  // diagonal or ragged tile: hide the keys this row must not see
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
+        for (int hb = 0; hb < 2; ++hb) {
+          mbar_wait(bar(L::kBarSFull + 2 * t + hb), j & 1, wc, kErrWaitS);
+          tc_fence_after();
+          if (r == 0) MA_STAMP(t, 1);
+          uint32_t s[2][32];
+          tmem_ld32(tS + hb * kHalfN, s[0]);
+          tmem_ld32(tS + hb * kHalfN + 32, s[1]);
+          tmem_wait_ld();
+          if (r == 0) MA_STAMP(t, 2);
+          if constexpr (QK8) {
+            // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding
+            // the bit pattern of 1.5*2^23 and subtracting that value is exact.
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (q * 32 + i >= lim) s[q][i] = __float_as_uint(-INFINITY);
-        }
-        // row maximum: four independent chains of 3-input max
-        float mx4[4];
+            for (int q = 0; q < 2; ++q)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float m = fmaxf(__uint_as_float(s[q][0]), __uint_as_float(s[q][1]));
-#pragma unroll
-          for (int i = 2; i < 32; i += 2)
-            m = fmax3(m, __uint_as_float(s[q][i]), __uint_as_float(s[q][i + 1]));
-          mx4[q] = m;
-        }
-        // running maximum m_cur is kept in log2 units (raw maximum * cj)
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * cj;
-        float alpha = 1.f;
-        if (j == 0) {
-          m_cur = mx;
-        } else {
-          const float m_new = fmaxf(m_cur, mx);
-          if (m_new - m_cur > kLazyThreshold) {  // also taken when m_cur = -inf
-            alpha = ex2(m_cur - m_new);
-            m_cur = m_new;
+              for (int i = 0; i < 32; ++i)
+                s[q][i] = __float_as_uint(__uint_as_float(s[q][i] + 0x4B400000u) - 12582912.f);
           }
-        }
-        alpha_smem[t * kTileM + r] = alpha;
-        warp_arrive(bar(L::kBarAlpha + t));
-        if (r == 0) MA_STAMP(t, 3);
-
-        const float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
-        float psum0 = 0.f, psum1 = 0.f;
+          const int lim = vis_row - j * kTileN - hb * kHalfN;
+          if (lim < kHalfN) {  // diagonal or ragged half: hide the keys this row must not see
 #pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {  // 64 keys -> 32 packed columns per TMEM store
+            for (int q = 0; q < 2; ++q)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (q * 32 + i >= lim) s[q][i] = __float_as_uint(-INFINITY);
+          }
+          // row maximum of the half: four independent chains of 3-input max
+          float mx4[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t* sp = &s[q >> 1][(q & 1) * 16];
+            float m = fmaxf(__uint_as_float(sp[0]), __uint_as_float(sp[1]));
+#pragma unroll
+            for (int i = 2; i < 16; i += 2) m = fmax3(m, __uint_as_float(sp[i]), __uint_as_float(sp[i + 1]));
+            mx4[q] = m;
+          }
+          // running maximum m_cur is kept in log2 units (raw maximum * cj)
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * cj;
+          float alpha = 1.f;
+          if (j == 0 && hb == 0) {
+            m_cur = mx;
+          } else {
+            const float m_new = fmaxf(m_cur, mx);
+            if (m_new - m_cur > kLazyThreshold) {  // also taken when m_cur = -inf
+              alpha = ex2(m_cur - m_new);
+              m_cur = m_new;
+            }
+          }
+          alpha_smem[(2 * t + hb) * kTileM + r] = alpha;
+          warp_arrive(bar(L::kBarAlpha + 2 * t + hb));
+          if (r == 0) MA_STAMP(t, 3);
+
+          const float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
+          float psum0 = 0.f, psum1 = 0.f;
           uint32_t pk[32];
 #pragma unroll
-          for (int qq = 0; qq < 2; ++qq) {
-            const int q = hb * 2 + qq;
+          for (int q = 0; q < 2; ++q)
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               const float p0 = ex2(fmaf(__uint_as_float(s[q][i]), cj, -mc));
               const float p1 = ex2(fmaf(__uint_as_float(s[q][i + 1]), cj, -mc));
               psum0 += p0;
               psum1 += p1;
-              pk[qq * 16 + (i >> 1)] = pack2<BF16>(p0, p1);
+              pk[q * 16 + (i >> 1)] = pack2<BF16>(p0, p1);
             }
-          }
-          tmem_st32(tS + hb * 32, pk);
-          // publish each half as soon as it is in TMEM: the PV MMAs of the first 64 keys
-          // run while the second half is still being exponentiated
+          l_run = l_run * alpha + (psum0 + psum1);
+          tmem_st32(tS + hb * kHalfN, pk);  // P of this half over the first 32 columns of its S
           tmem_wait_st();
           tc_fence_before();
           warp_arrive(bar(L::kBarPReady + 2 * t + hb));
           if (r == 0) MA_STAMP(t, 4);
         }
-        l_run = l_run * alpha + (psum0 + psum1);
-        if (r == 0) MA_STAMP(t, 5);
       }
 
       l_smem[t * kTileM + r] = l_run;
@@ -304,28 +306,31 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int r = tid & 127;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     for (int j = 0; j < n_tiles; ++j) {
-      for (int t = 0; t < nt; ++t) {
-        mbar_wait(bar(L::kBarAlpha + t), j & 1, wc, kErrWaitCorr);
-        if (r == 0) MA_STAMP(2, 20 + t);
-        const float alpha = alpha_smem[t * kTileM + r];
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          mbar_wait(bar(L::kBarODone + t), (j - 1) & 1, wc, kErrWaitO);
-          tc_fence_after();
-          const uint32_t tO = tmem_base + (t ? L::kColO1 : L::kColO0) + lane_off;
 #pragma unroll
-          for (int q = 0; q < D / 32; ++q) {
-            uint32_t o[32];
-            tmem_ld32(tO + q * 32, o);
-            tmem_wait_ld();
+      for (int hb = 0; hb < 2; ++hb) {
+        for (int t = 0; t < nt; ++t) {
+          mbar_wait(bar(L::kBarAlpha + 2 * t + hb), j & 1, wc, kErrWaitCorr);
+          const float alpha = alpha_smem[(2 * t + hb) * kTileM + r];
+          if ((j > 0 || hb > 0) && __any_sync(0xffffffffu, alpha != 1.f)) {
+            // every PV issued so far into O_t must have finished: the previous half-step's
+            if (hb == 0) mbar_wait(bar(L::kBarODone + 2 * t + 1), (j - 1) & 1, wc, kErrWaitO);
+            else mbar_wait(bar(L::kBarODone + 2 * t + 0), j & 1, wc, kErrWaitO);
+            tc_fence_after();
+            const uint32_t tO = tmem_base + L::kColO + D * t + lane_off;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + q * 32, o);
+            for (int q = 0; q < D / 32; ++q) {
+              uint32_t o[32];
+              tmem_ld32(tO + q * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + q * 32, o);
+            }
+            tmem_wait_st();
+            tc_fence_before();
           }
-          tmem_wait_st();
-          tc_fence_before();
+          warp_arrive(bar(L::kBarOReady + 2 * t + hb));
         }
-        warp_arrive(bar(L::kBarOReady + t));
-        if (r == 0) MA_STAMP(2, 22 + t);
       }
     }
     // epilogue
@@ -335,10 +340,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         mbar_wait(bar(L::kBarLReady + t), 0, wc, kErrWaitCorr);
         const float l = l_smem[t * kTileM + r];
         inv_l = (l > 0.f) ? (1.f / l) : 0.f;
-        mbar_wait(bar(L::kBarODone + t), (n_tiles - 1) & 1, wc, kErrWaitO);
+        mbar_wait(bar(L::kBarODone + 2 * t + 1), (n_tiles - 1) & 1, wc, kErrWaitO);
         tc_fence_after();
       }
-      const uint32_t tO = tmem_base + (t ? L::kColO1 : L::kColO0) + lane_off;
+      const uint32_t tO = tmem_base + L::kColO + D * t + lane_off;
       const uint32_t stage = sQ + t * L::kTileBytes;
 #pragma unroll
       for (int q = 0; q < D / 32; ++q) {
@@ -382,47 +387,57 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     tc_fence_before();
   } else {
     reg_dec<MA_REG_OTHER>();
-    if (warp == 12) {
-      // =========================== MMA issuer ======================================
-      // One thread issues every tcgen05.mma, strictly alternating the two Q tiles:
-      // PV0(j) S0(j+1) PV1(j) S1(j+1).  The alternation keeps the two softmax groups half a
-      // period apart, so one exponentiates while the other owns the tensor pipe.
-      if (lane == 0 && n_tiles > 0) {
+    if (warp == 12 || warp == 14) {
+      // =========================== MMA issuers =====================================
+      // One issuing thread per Q tile (warp 12 -> tile 0, warp 14 -> tile 1).  Each walks its
+      // tile's halves in the order the softmax group publishes them: PV_a(j) S_a(j+1) PV_b(j)
+      // S_b(j+1).  The tensor pipe interleaves the two streams.
+      const int t = (warp == 12) ? 0 : 1;
+      if (lane == 0 && n_tiles > 0 && t < nt) {
         // kind::f16: D fmt f32, A/B f16 or bf16.  kind::i8: D fmt s32 (2), A/B signed int8 (1).
         constexpr uint32_t idesc_s =
-            QK8 ? make_idesc(2, 1, 0, 0, kTileM, kTileN) : make_idesc(1, BF16 ? 1 : 0, 0, 0, kTileM, kTileN);
+            QK8 ? make_idesc(2, 1, 0, 0, kTileM, kHalfN) : make_idesc(1, BF16 ? 1 : 0, 0, 0, kTileM, kHalfN);
         constexpr uint32_t idesc_o = make_idesc(1, BF16 ? 1 : 0, 0, 1, kTileM, D);
-        const uint32_t tS[2] = {tmem_base + L::kColS0, tmem_base + L::kColS1};
-        const uint32_t tO[2] = {tmem_base + L::kColO0, tmem_base + L::kColO1};
-        auto issue_s = [&](int t, int slot) {
+        const uint32_t sQt = sQ + t * L::kTileBytes;
+        const uint32_t tO = tmem_base + L::kColO + D * t;
+        const uint32_t tSt = tmem_base + L::kColS + 128 * t;
+        // S(half) = Q_t . K[64*half .. 64*half+64)^T  ->  TMEM columns [128t + 64half, +64)
+        auto issue_s = [&](int hb, int slot) {
+          const uint32_t d_tmem = tSt + kHalfN * hb;
           if constexpr (QK8) {
             // int8 rows are D bytes: 64-byte swizzle (8 rows = 512 B) at D=64, 128-byte at D=128;
             // one MMA consumes K = 32 bytes.
             constexpr uint32_t kLayout = (D == 64) ? 4u : 2u;
             constexpr uint32_t kSbo = (D == 64) ? 512u : 1024u;
+            const uint32_t kb = sRing + slot * L::kTileBytes + hb * kHalfN * D;
 #pragma unroll
             for (int k = 0; k < D / 32; ++k) {
-              const uint64_t da = make_smem_desc(sQ + t * L::kTileBytes + k * 32, 16, kSbo, kLayout);
-              const uint64_t db = make_smem_desc(sRing + slot * L::kTileBytes + k * 32, 16, kSbo, kLayout);
-              mma_i8_ss(tS[t], da, db, idesc_s, k > 0);
+              const uint64_t da = make_smem_desc(sQt + k * 32, 16, kSbo, kLayout);
+              const uint64_t db = make_smem_desc(kb + k * 32, 16, kSbo, kLayout);
+              mma_i8_ss(d_tmem, da, db, idesc_s, k > 0);
             }
           } else {
+            const uint32_t kb = sRing + slot * L::kTileBytes + hb * kHalfN * 128;
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
               const uint32_t off = (k / 4) * kBoxBytes + (k % 4) * 32;
-              const uint64_t da = make_smem_desc(sQ + t * L::kTileBytes + off, 16, 1024);
-              const uint64_t db = make_smem_desc(sRing + slot * L::kTileBytes + off, 16, 1024);
-              mma_f16_ss(tS[t], da, db, idesc_s, k > 0);
+              const uint64_t da = make_smem_desc(sQt + off, 16, 1024);
+              const uint64_t db = make_smem_desc(kb + off, 16, 1024);
+              mma_f16_ss(d_tmem, da, db, idesc_s, k > 0);
             }
           }
         };
-        for (int t = 0; t < nt; ++t) mbar_wait(bar(L::kBarQFull + t), 0, wc, kErrWaitKV);
+        mbar_wait(bar(L::kBarQFull + t), 0, wc, kErrWaitKV);
         int cons = 0;  // ring consumption index: K_0, V_0, K_1, V_1, ...
         mbar_wait(bar(L::kBarKvFull + 0), 0, wc, kErrWaitKV);
+        // Start tile 1 about half a softmax step after tile 0 (when tile 0 has published its
+        // first P): the two softmax groups then alternate between their max and exp2 phases
+        // instead of competing for the exp2 unit at the same moments.
+        if (t == 1) mbar_wait(bar(L::kBarAlpha + 0), 0, wc, kErrWaitP);
         tc_fence_after();
-        for (int t = 0; t < nt; ++t) {
-          issue_s(t, 0);
-          mma_commit(bar(L::kBarSFull + t));
+        for (int hb = 0; hb < 2; ++hb) {
+          issue_s(hb, 0);
+          mma_commit(bar(L::kBarSFull + 2 * t + hb));
         }
         mma_commit(bar(L::kBarKvEmpty + 0));
         cons = 1;
@@ -433,35 +448,33 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const bool has_next = (j + 1 < n_tiles);
           const int kslot = cons % L::kStages;
           const uint32_t kpar = (cons / L::kStages) & 1;
-          for (int t = 0; t < nt; ++t) {
-            MA_STAMP(3, 10 + t);
-            mbar_wait(bar(L::kBarOReady + t), j & 1, wc, kErrWaitCorr);
 #pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-              mbar_wait(bar(L::kBarPReady + 2 * t + hb), j & 1, wc, kErrWaitP);
-              tc_fence_after();
-              MA_STAMP(3, 12 + 2 * hb + t);
+          for (int hb = 0; hb < 2; ++hb) {
+            MA_STAMP(3 + t, 10 + hb);
+            mbar_wait(bar(L::kBarOReady + 2 * t + hb), j & 1, wc, kErrWaitCorr);
+            mbar_wait(bar(L::kBarPReady + 2 * t + hb), j & 1, wc, kErrWaitP);
+            tc_fence_after();
+            MA_STAMP(3 + t, 14 + hb);
+            const uint32_t tP = tSt + kHalfN * hb;
 #pragma unroll
-              for (int kk = 0; kk < kTileN / 32; ++kk) {
-                const int k = hb * (kTileN / 32) + kk;
-                const uint64_t db =
-                    make_smem_desc(sRing + vslot * L::kTileBytes + k * 2048, kBoxBytes, 1024);
-                mma_f16_ts(tO[t], tS[t] + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-              }
+            for (int kk = 0; kk < kHalfN / 16; ++kk) {
+              const int k = hb * (kHalfN / 16) + kk;  // 16-key slice of the V tile
+              const uint64_t db =
+                  make_smem_desc(sRing + vslot * L::kTileBytes + k * 2048, kBoxBytes, 1024);
+              mma_f16_ts(tO, tP + kk * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
             }
-            mma_commit(bar(L::kBarODone + t));
-            if (t == nt - 1) mma_commit(bar(L::kBarKvEmpty + vslot));
-            MA_STAMP(3, 18 + t);
+            mma_commit(bar(L::kBarODone + 2 * t + hb));
+            if (hb == 1) mma_commit(bar(L::kBarKvEmpty + vslot));
             if (has_next) {
-              if (t == 0) {
+              if (hb == 0) {
                 mbar_wait(bar(L::kBarKvFull + kslot), kpar, wc, kErrWaitKV);
                 tc_fence_after();
               }
-              issue_s(t, kslot);
-              mma_commit(bar(L::kBarSFull + t));
-              MA_STAMP(3, 16 + t);
-              if (t == nt - 1) mma_commit(bar(L::kBarKvEmpty + kslot));
+              issue_s(hb, kslot);
+              mma_commit(bar(L::kBarSFull + 2 * t + hb));
+              if (hb == 1) mma_commit(bar(L::kBarKvEmpty + kslot));
             }
+            MA_STAMP(3 + t, 18 + hb);
           }
           if (has_next) ++cons;
         }
