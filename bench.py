@@ -309,8 +309,10 @@ def main():
         n_tasks = sum(len(par.ring_step_tasks(rank, world, s_, causal)) for s_ in range(world))
         launches_per_step = 2 * n_tasks  # one attention + one merge launch per task
 
+        ring_out = [o]
+
         def attend():
-            o.copy_(par.ring_forward(q, k, v, causal=causal, rank=rank, world=world))
+            ring_out[0] = par.ring_forward(q, k, v, causal=causal, rank=rank, world=world)
     else:
         def attend():
             miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel)
@@ -323,7 +325,7 @@ def main():
         k.copy_(hk, non_blocking=True)
         v.copy_(hv, non_blocking=True)
         attend()
-        ho.copy_(o, non_blocking=True)
+        ho.copy_(ring_out[0] if ring else o, non_blocking=True)
 
     def barrier():
         if world > 1:

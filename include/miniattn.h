@@ -152,6 +152,9 @@ typedef struct MiniAttnMergeParams {
   int32_t D;
   int32_t dtype;          /* dtype of part_o / out: MINIATTN_FP16 | MINIATTN_BF16       */
   int32_t init;           /* 1: acc := partial (acc_o / acc_lse are not read)           */
+  int64_t out_rows_per_slab; /* 0: `out` is contiguous.  > 0: `out` is a token-range view of  */
+  int64_t out_slab_stride;   /* a larger tensor: consecutive groups of out_rows_per_slab rows */
+                             /* (one (batch, head) each) start out_slab_stride elements apart */
 } MiniAttnMergeParams;
 
 int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream);

@@ -33,7 +33,8 @@ cudaError_t launch_quant_qk_static(int D, bool bf16, const void* q, const long l
 cudaError_t launch_wait_selftest(int32_t* status, unsigned long long limit_ns, cudaStream_t st);
 cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part_o,
                                   const float* part_lse, void* out, long long rows, int D, bool bf16,
-                                  int init, int sm_count, cudaStream_t st);
+                                  int init, long long rows_per_slab, long long out_slab_stride,
+                                  int sm_count, cudaStream_t st);
 }  // namespace ma
 
 namespace {
@@ -363,8 +364,18 @@ int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream) {
     return fail(MINIATTN_EINVAL, "acc_o, part_o and out must be 16-byte aligned");
   int sms = 0, rc;
   if ((rc = check_device(&sms)) != 0) return rc;
+  long long rows_per_slab = p->rows, slab_stride = p->rows * p->D;
+  if (p->out_rows_per_slab > 0) {
+    if (p->rows % p->out_rows_per_slab != 0)
+      return fail(MINIATTN_EINVAL, "rows must be a multiple of out_rows_per_slab");
+    if (p->out_slab_stride < p->out_rows_per_slab * p->D || p->out_slab_stride % 8 != 0)
+      return fail(MINIATTN_EINVAL, "out_slab_stride must be a multiple of 8 elements and cover a slab");
+    rows_per_slab = p->out_rows_per_slab;
+    slab_stride = p->out_slab_stride;
+  }
   cudaError_t e = ma::launch_merge_partials(p->acc_o, p->acc_lse, p->part_o, p->part_lse, p->out,
-                                            p->rows, p->D, p->dtype == MINIATTN_BF16, p->init, sms,
+                                            p->rows, p->D, p->dtype == MINIATTN_BF16, p->init,
+                                            rows_per_slab, slab_stride, sms,
                                             reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));

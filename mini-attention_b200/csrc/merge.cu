@@ -41,7 +41,8 @@ template <int VEC, bool BF16>
 __global__ void __launch_bounds__(256)
 merge_partials_kernel(float* __restrict__ acc_o, float* __restrict__ acc_lse,
                       const uint16_t* __restrict__ part_o, const float* __restrict__ part_lse,
-                      uint16_t* __restrict__ out, long long rows, int init) {
+                      uint16_t* __restrict__ out, long long rows, int init, long long rows_per_slab,
+                      long long out_slab_stride) {
   constexpr int D = 32 * VEC;
   const int lane = threadIdx.x & 31;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -90,13 +91,16 @@ merge_partials_kernel(float* __restrict__ acc_o, float* __restrict__ acc_lse,
     }
     if (lane == 0) acc_lse[row] = lse_new;
     if (out != nullptr) {
+      // `out` may be a token-range view of a larger tensor: slabs of rows_per_slab rows (one
+      // (batch, head) each) lie out_slab_stride elements apart
+      uint16_t* orow = out + (row / rows_per_slab) * out_slab_stride + (row % rows_per_slab) * D;
       if constexpr (VEC == 4) {
         uint2 w;
         w.x = pack2f<BF16>(r[0], r[1]);
         w.y = pack2f<BF16>(r[2], r[3]);
-        *reinterpret_cast<uint2*>(out + row * D + lane * 4) = w;
+        *reinterpret_cast<uint2*>(orow + lane * 4) = w;
       } else {
-        *reinterpret_cast<uint32_t*>(out + row * D + lane * 2) = pack2f<BF16>(r[0], r[1]);
+        *reinterpret_cast<uint32_t*>(orow + lane * 2) = pack2f<BF16>(r[0], r[1]);
       }
     }
   }
@@ -104,7 +108,8 @@ merge_partials_kernel(float* __restrict__ acc_o, float* __restrict__ acc_lse,
 
 cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part_o,
                                   const float* part_lse, void* out, long long rows, int D, bool bf16,
-                                  int init, int sm_count, cudaStream_t st) {
+                                  int init, long long rows_per_slab, long long out_slab_stride,
+                                  int sm_count, cudaStream_t st) {
   if (rows == 0) return cudaSuccess;
   const long long blocks_needed = (rows + 7) / 8;  // 8 warps (rows) per 256-thread block
   const long long cap = static_cast<long long>(sm_count) * 8;  // grid: multiple of the SM count
@@ -112,11 +117,11 @@ cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part
   const uint16_t* po = static_cast<const uint16_t*>(part_o);
   uint16_t* oo = static_cast<uint16_t*>(out);
   if (D == 128) {
-    if (bf16) merge_partials_kernel<4, true><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init);
-    else merge_partials_kernel<4, false><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init);
+    if (bf16) merge_partials_kernel<4, true><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init, rows_per_slab, out_slab_stride);
+    else merge_partials_kernel<4, false><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init, rows_per_slab, out_slab_stride);
   } else if (D == 64) {
-    if (bf16) merge_partials_kernel<2, true><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init);
-    else merge_partials_kernel<2, false><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init);
+    if (bf16) merge_partials_kernel<2, true><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init, rows_per_slab, out_slab_stride);
+    else merge_partials_kernel<2, false><<<grid, 256, 0, st>>>(acc_o, acc_lse, po, part_lse, oo, rows, init, rows_per_slab, out_slab_stride);
   } else {
     return cudaErrorInvalidValue;
   }

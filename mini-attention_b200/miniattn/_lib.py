@@ -48,6 +48,7 @@ class MergeParams(C.Structure):
         ("acc_o", C.c_void_p), ("acc_lse", C.c_void_p), ("part_o", C.c_void_p),
         ("part_lse", C.c_void_p), ("out", C.c_void_p),
         ("rows", C.c_int64), ("D", C.c_int32), ("dtype", C.c_int32), ("init", C.c_int32),
+        ("out_rows_per_slab", C.c_int64), ("out_slab_stride", C.c_int64),
     ]
 
 

@@ -215,16 +215,27 @@ def merge_partials(
     acc_o fp32 (..., N, D) and acc_lse fp32 (..., N) are updated; part_o is the fp16/bf16
     normalised partial with its part_lse.  ``init=True`` overwrites the accumulators with the
     partial; ``out`` (same dtype as part_o) additionally receives the merged result.  All
-    tensors must be contiguous CUDA tensors of matching shapes.
+    tensors must be contiguous CUDA tensors of matching shapes, except ``out``, which may be a
+    token-range view ``big[:, :, a:b]`` of a contiguous (B,H,N,D) tensor.
     """
     if part_o.dtype not in _DTYPES:
         raise RuntimeError("Only fp16 and bf16 partials are supported")
     if acc_o.dtype != torch.float32 or acc_lse.dtype != torch.float32 or part_lse.dtype != torch.float32:
         raise RuntimeError("acc_o, acc_lse and part_lse must be fp32")
-    tensors = [acc_o, acc_lse, part_o, part_lse] + ([out] if out is not None else [])
-    for t in tensors:
+    for t in (acc_o, acc_lse, part_o, part_lse):
         if not t.is_cuda or not t.is_contiguous() or t.device != acc_o.device:
             raise RuntimeError("merge_partials takes contiguous CUDA tensors on one device")
+    slab_rows = slab_stride = 0
+    if out is not None:
+        if not out.is_cuda or out.device != acc_o.device:
+            raise RuntimeError("out must be a CUDA tensor on the same device")
+        if not out.is_contiguous():
+            # accept (B,H,n,D) views whose (batch, head) slabs are evenly spaced
+            ok = (out.dim() == 4 and out.stride(3) == 1 and out.stride(2) == out.shape[3]
+                  and out.stride(0) == out.stride(1) * out.shape[1])
+            if not ok:
+                raise RuntimeError("out must be contiguous or a token-range view of a contiguous (B,H,N,D) tensor")
+            slab_rows, slab_stride = out.shape[2], out.stride(1)
     if acc_o.shape != part_o.shape or acc_lse.shape != part_lse.shape or acc_lse.shape != acc_o.shape[:-1]:
         raise RuntimeError("shape mismatch between accumulators and partials")
     if out is not None and (out.shape != part_o.shape or out.dtype != part_o.dtype):
@@ -237,6 +248,7 @@ def merge_partials(
     p.D = acc_o.shape[-1]
     p.dtype = _DTYPES[part_o.dtype]
     p.init = 1 if init else 0
+    p.out_rows_per_slab, p.out_slab_stride = slab_rows, slab_stride
     with torch.cuda.device(acc_o.device):
         stream = torch.cuda.current_stream(acc_o.device).cuda_stream
         rc = _lib.lib.miniattn_merge_partials(C.byref(p), C.c_void_p(stream))

@@ -179,7 +179,6 @@ def ring_forward(
     for s in range(world):
         for t in ring_step_tasks(rank, world, s, causal):
             remaining[t.q_half] += 1
-    stage = [torch.empty((B, H, L, D), dtype=q_local.dtype, device=q_local.device) for _ in range(2)]
     for s in range(world):
         handle = None
         if s + 1 < world:
@@ -191,9 +190,8 @@ def ring_forward(
             o, lse = attn_fn(q_blocks[t.q_half], kb, vb, t.causal, t.q_block * L, t.kv_block * L, softmax_scale)
             remaining[t.q_half] -= 1
             last = remaining[t.q_half] == 0
-            accs[t.q_half].add(o, lse, out=stage[t.q_half] if last else None)
-            if last:
-                outs[t.q_half].copy_(stage[t.q_half])
+            # the last merge of a block writes the finished rows straight into the output
+            accs[t.q_half].add(o, lse, out=outs[t.q_half] if last else None)
         if handle is not None:
             handle.wait()
             k_cur, v_cur = bufs[s % 2]
