@@ -201,6 +201,81 @@ def flash_attn_fwd_int8qk(
     return (out, lse) if return_lse else out
 
 
+class HostPipeline:
+    """Forward attention on HOST (pinned) tensors with the copies overlapped with compute.
+
+    The (batch x KV-head group) units are independent, so the work is cut into chunks of units;
+    chunk i+1 is copied host->device on one stream while chunk i runs on the compute stream and
+    the output of chunk i-1 is copied back on a third stream.  Device staging tensors, streams and
+    events are created once per problem shape and reused.  Inputs: q (B,Hq,N,D), k/v (B,Hkv,N,D)
+    in pinned host memory; the result is written to ``out`` (pinned host tensor, same shape as q).
+    """
+
+    def __init__(self, q: torch.Tensor, k: torch.Tensor, device, n_chunks: int = 8):
+        self.device = torch.device(device)
+        B, Hq, Nq, D = q.shape
+        Hkv = k.shape[1]
+        self.G = Hq // Hkv
+        self.qd = torch.empty(q.shape, dtype=q.dtype, device=self.device)
+        self.kd = torch.empty(k.shape, dtype=k.dtype, device=self.device)
+        self.vd = torch.empty(k.shape, dtype=k.dtype, device=self.device)
+        self.od = torch.empty(q.shape, dtype=q.dtype, device=self.device)
+        # chunks: runs of KV heads inside one batch element
+        per = max(1, (B * Hkv + n_chunks - 1) // n_chunks)
+        self.chunks = []
+        for b in range(B):
+            for h0 in range(0, Hkv, per):
+                self.chunks.append((b, h0, min(Hkv, h0 + per)))
+        self.s_in = torch.cuda.Stream(self.device)
+        self.s_out = torch.cuda.Stream(self.device)
+        self.ev_in = [torch.cuda.Event() for _ in self.chunks]
+        self.ev_done = [torch.cuda.Event() for _ in self.chunks]
+
+    def __call__(self, q, k, v, out, *, causal=False, softmax_scale=None, kernel="auto"):
+        G = self.G
+        main = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(main)   # staging buffers may still be in use by earlier work
+        self.s_out.wait_stream(main)
+        for i, (b, h0, h1) in enumerate(self.chunks):
+            with torch.cuda.stream(self.s_in):
+                self.qd[b, h0 * G:h1 * G].copy_(q[b, h0 * G:h1 * G], non_blocking=True)
+                self.kd[b, h0:h1].copy_(k[b, h0:h1], non_blocking=True)
+                self.vd[b, h0:h1].copy_(v[b, h0:h1], non_blocking=True)
+                self.ev_in[i].record(self.s_in)
+            main.wait_event(self.ev_in[i])
+            flash_attn_fwd(self.qd[b:b + 1, h0 * G:h1 * G], self.kd[b:b + 1, h0:h1], self.vd[b:b + 1, h0:h1],
+                           causal=causal, softmax_scale=softmax_scale, kernel=kernel,
+                           out=self.od[b:b + 1, h0 * G:h1 * G])
+            self.ev_done[i].record(main)
+            self.s_out.wait_event(self.ev_done[i])
+            with torch.cuda.stream(self.s_out):
+                out[b, h0 * G:h1 * G].copy_(self.od[b, h0 * G:h1 * G], non_blocking=True)
+        main.wait_stream(self.s_out)
+        return out
+
+
+_host_pipelines: dict = {}
+
+
+def flash_attn_fwd_host(q, k, v, out=None, *, causal=False, softmax_scale=None, device=None, n_chunks=8,
+                        kernel="auto"):
+    """Forward attention with q, k, v and the result in pinned HOST memory ((B,H,N,D) layout).
+    Host<->device copies are overlapped with the kernel chunk by chunk (see :class:`HostPipeline`);
+    the call returns once everything is enqueued — synchronise before reading ``out``."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.is_cuda or not t.is_pinned():
+            raise RuntimeError(f"{name} must be a pinned host tensor")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if out is None:
+        out = torch.empty_like(q).pin_memory()
+    key = (tuple(q.shape), tuple(k.shape), q.dtype, device.index, n_chunks)
+    pipe = _host_pipelines.get(key)
+    if pipe is None:
+        pipe = _host_pipelines[key] = HostPipeline(q, k, device, n_chunks)
+    with torch.cuda.device(device):
+        return pipe(q, k, v, out, causal=causal, softmax_scale=softmax_scale, kernel=kernel)
+
+
 def merge_partials(
     acc_o: torch.Tensor,
     acc_lse: torch.Tensor,

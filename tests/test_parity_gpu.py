@@ -243,3 +243,16 @@ def test_variant_modules_match_reference_math():
     assert y0.shape == y1.shape == (2, 256, 512) and not torch.equal(y0, y1)
     with pytest.raises(RuntimeError, match="lower-triangular"):
         mha(x.to(DEV), mask=torch.ones(256, 256, device=DEV))
+
+
+def test_host_buffer_pipeline():
+    """flash_attn_fwd_host: pinned host tensors in and out, chunked copies overlapped with compute."""
+    q, k, v = make_inputs(2, 8, 2, 512, 512, 128, torch.float16, seed=21)
+    ref = attention_reference(q, k, v, causal=True, out_dtype=torch.float32)
+    qh, kh, vh = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    for _ in range(2):  # second call reuses the cached pipeline
+        out = miniattn.flash_attn_fwd_host(qh, kh, vh, causal=True, n_chunks=3)
+        torch.cuda.synchronize()
+        assert not out.is_cuda and maxerr(out, ref) <= TOL[torch.float16]
+    with pytest.raises(RuntimeError, match="pinned"):
+        miniattn.flash_attn_fwd_host(q, kh, vh)
