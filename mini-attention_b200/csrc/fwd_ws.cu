@@ -4,10 +4,10 @@
 // the reference mainloop (kernels/flash_attn/cuda/sm_120/kernel/include/forward_kernel.cuh:137-221
 // and softmax.cuh:29-138), restructured for tcgen05 / TMEM / TMA:
 //
-//   warps 0-3   softmax of Q tile 0   (thread = one query row; S row read from TMEM)
-//   warps 4-7   softmax of Q tile 1
-//   warps 8-11  correction: rescales the O accumulators in TMEM when a row maximum moved,
-//               and runs the epilogue (O / l -> 16 bit -> swizzled smem -> TMA store)
+//   warps 0-3   softmax of Q tile 0   (thread = one query row; S row read from TMEM), then its
+//               epilogue (O / l -> 16 bit -> swizzled smem -> TMA store)
+//   warps 4-7   softmax and epilogue of Q tile 1
+//   warps 8-11  correction: rescales the O accumulators in TMEM when a row maximum moved (rare)
 //   warp 12     MMA issuer of Q tile 0 (one thread issues its tcgen05.mma stream)
 //   warp 14     MMA issuer of Q tile 1
 //   warp 13     TMA producer: Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring
@@ -75,6 +75,7 @@ struct WsLayout {
   static constexpr int kColO = 256;   // O accumulator of tile t at kColO + D*t
 };
 
+constexpr int kBarEpilogue = 1;  // named barriers 1 and 2: epilogue of softmax group 0 / 1
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -121,7 +122,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t sQ = sbase + L::kOffQ;
   const uint32_t sRing = sbase + L::kOffRing;
   float* alpha_smem = reinterpret_cast<float*>(gbase + L::kOffAlpha);
-  float* l_smem = reinterpret_cast<float*>(gbase + L::kOffL);
   const uint32_t bars = sbase + L::kOffBar;
   auto bar = [&](int idx) -> uint32_t { return bars + 8u * idx; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kOffMisc);
@@ -165,8 +165,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(bar(L::kBarOReady + i), 4);
       mbar_init(bar(L::kBarODone + i), 1);
     }
-    mbar_init(bar(L::kBarLReady + 0), 4);
-    mbar_init(bar(L::kBarLReady + 1), 4);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_q);
@@ -293,53 +291,14 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
 
-      l_smem[t * kTileM + r] = l_run;
-      warp_arrive(bar(L::kBarLReady + t));
       if (a.lse != nullptr && row < a.Nq) {
         const float lse = (l_run > 0.f) ? (m_cur * 0.6931471805599453f + __logf(l_run)) : -INFINITY;
         a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] = lse;
       }
-    }
-  } else if (warp < 12) {
-    // =========================== correction + epilogue =============================
-    reg_dec<MA_REG_CORR>();
-    const int r = tid & 127;
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    for (int j = 0; j < n_tiles; ++j) {
-#pragma unroll
-      for (int hb = 0; hb < 2; ++hb) {
-        for (int t = 0; t < nt; ++t) {
-          mbar_wait(bar(L::kBarAlpha + 2 * t + hb), j & 1, wc, kErrWaitCorr);
-          const float alpha = alpha_smem[(2 * t + hb) * kTileM + r];
-          if ((j > 0 || hb > 0) && __any_sync(0xffffffffu, alpha != 1.f)) {
-            // every PV issued so far into O_t must have finished: the previous half-step's
-            if (hb == 0) mbar_wait(bar(L::kBarODone + 2 * t + 1), (j - 1) & 1, wc, kErrWaitO);
-            else mbar_wait(bar(L::kBarODone + 2 * t + 0), j & 1, wc, kErrWaitO);
-            tc_fence_after();
-            const uint32_t tO = tmem_base + L::kColO + D * t + lane_off;
-#pragma unroll
-            for (int q = 0; q < D / 32; ++q) {
-              uint32_t o[32];
-              tmem_ld32(tO + q * 32, o);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(tO + q * 32, o);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-          }
-          warp_arrive(bar(L::kBarOReady + 2 * t + hb));
-        }
-      }
-    }
-    // epilogue
-    for (int t = 0; t < nt; ++t) {
-      float inv_l = 0.f;
+      // ---- epilogue of this Q tile (the two softmax groups run theirs side by side):
+      //      O / l -> 16 bit -> swizzled smem (the tile's Q buffer) -> TMA store
+      const float inv_l = (l_run > 0.f) ? (1.f / l_run) : 0.f;
       if (n_tiles > 0) {
-        mbar_wait(bar(L::kBarLReady + t), 0, wc, kErrWaitCorr);
-        const float l = l_smem[t * kTileM + r];
-        inv_l = (l > 0.f) ? (1.f / l) : 0.f;
         mbar_wait(bar(L::kBarODone + 2 * t + 1), (n_tiles - 1) & 1, wc, kErrWaitO);
         tc_fence_after();
       }
@@ -375,15 +334,49 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
       fence_proxy_async_smem();
-      named_bar_sync(1, 128);
+      named_bar_sync(kBarEpilogue + t, 128);
       if (r == 0) {
 #pragma unroll
         for (int bx = 0; bx < L::kBoxes; ++bx)
           tma_store_4d(&tm_o, stage + bx * kBoxBytes, bx * kBoxCols, q0 + t * kTileM, h, b);
         tma_store_commit();
+        tma_store_wait_all();
+      }
+      tc_fence_before();
+    }
+  } else if (warp < 12) {
+    // =========================== correction ========================================
+    reg_dec<MA_REG_CORR>();
+    const int r = tid & 127;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    for (int j = 0; j < n_tiles; ++j) {
+#pragma unroll
+      for (int hb = 0; hb < 2; ++hb) {
+        for (int t = 0; t < nt; ++t) {
+          mbar_wait(bar(L::kBarAlpha + 2 * t + hb), j & 1, wc, kErrWaitCorr);
+          const float alpha = alpha_smem[(2 * t + hb) * kTileM + r];
+          if ((j > 0 || hb > 0) && __any_sync(0xffffffffu, alpha != 1.f)) {
+            // every PV issued so far into O_t must have finished: the previous half-step's
+            if (hb == 0) mbar_wait(bar(L::kBarODone + 2 * t + 1), (j - 1) & 1, wc, kErrWaitO);
+            else mbar_wait(bar(L::kBarODone + 2 * t + 0), j & 1, wc, kErrWaitO);
+            tc_fence_after();
+            const uint32_t tO = tmem_base + L::kColO + D * t + lane_off;
+#pragma unroll
+            for (int q = 0; q < D / 32; ++q) {
+              uint32_t o[32];
+              tmem_ld32(tO + q * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + q * 32, o);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+          }
+          warp_arrive(bar(L::kBarOReady + 2 * t + hb));
+        }
       }
     }
-    if (r == 0) tma_store_wait_all();
     tc_fence_before();
   } else {
     reg_dec<MA_REG_OTHER>();
