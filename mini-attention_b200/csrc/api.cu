@@ -20,7 +20,7 @@ cudaError_t launch_fwd_simple(int D, bool bf16, const CUtensorMap* tm, const Fwd
 cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
                           cudaStream_t st);
 cudaError_t launch_fwd_ws_int8qk(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
-                                 cudaStream_t st);
+                                 int sm_count, cudaStream_t st);
 cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs, const void* k,
                             const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk, float q_fold,
                             int8_t* q8, int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
@@ -184,6 +184,7 @@ static void fill_args(const MiniAttnFwdParams* p, ma::FwdArgs* a) {
   a->scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)p->D);
   a->scale_log2 = a->scale * 1.4426950408889634f;
   a->n_q_tiles = (p->Nq + ma::kTileM - 1) / ma::kTileM;
+  a->n_pair_items = 0;  // set by the warp-specialised launcher
   a->sq = nullptr;
   a->sk = nullptr;
   a->trace = nullptr;
@@ -343,7 +344,7 @@ int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream) {
   fill_args(&f, &a);
   a.sq = p->q_scale;
   a.sk = p->k_scale;
-  cudaError_t e = ma::launch_fwd_ws_int8qk(f.D, f.dtype == MINIATTN_BF16, tm, a,
+  cudaError_t e = ma::launch_fwd_ws_int8qk(f.D, f.dtype == MINIATTN_BF16, tm, a, sms,
                                            reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));

@@ -15,6 +15,8 @@ struct FwdArgs {
   float scale;         // softmax scale
   float scale_log2;    // softmax scale * log2(e)
   int n_q_tiles;       // ceil(Nq / 128)
+  int n_pair_items;    // warp-specialised kernel: CTAs [0, n_pair_items) take two Q tiles each,
+                       // the CTAs after them one Q tile each (the tail of the last wave)
   const float* sq;     // INT8-QK: [B, Hq,  ceil(Nq/128)] Q scales (softmax scale * log2e folded in)
   const float* sk;     // INT8-QK: [B, Hkv, ceil(Nk/128)] K scales
   unsigned long long* trace;  // debug builds only (MA_TRACE): per-role clock stamps of CTA 0

@@ -28,6 +28,8 @@
 // The row maximum is updated lazily: a row keeps exponentiating against a stale maximum until the
 // true maximum has grown by more than 2^8 (in the exp2 domain), so the O accumulator is rescaled
 // only rarely; l is accumulated against the same maximum, which keeps O / l exact.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -132,20 +134,29 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int lane = tid & 31;
 
   // ---- work item: heaviest (latest) Q tile pairs first; heads of one pair adjacent ----
+  // CTAs past n_pair_items take a single Q tile: the launcher cuts the pairs that would form a
+  // less-than-half-full last wave into two CTAs each, so that the wave ends sooner.
   const int n_pairs = (a.n_q_tiles + 1) >> 1;
   const int bh_total = a.Hq * a.B;
-  const int item = blockIdx.x;
+  int item = blockIdx.x;
+  int single = -1;  // which tile of its pair a single-tile CTA takes
+  if (item >= a.n_pair_items) {
+    const int s_idx = item - a.n_pair_items;
+    item = a.n_pair_items + (s_idx >> 1);
+    single = s_idx & 1;
+  }
   const int pair = n_pairs - 1 - item / bh_total;
   const int bh = item % bh_total;
   const int h = bh % a.Hq;
   const int b = bh / a.Hq;
   const int hk = h / (a.Hq / a.Hkv);
-  const int q0 = pair * 2 * kTileM;
-  const int nt = (q0 + kTileM < a.Nq) ? 2 : 1;  // Q tiles of this item that hold real rows
+  const int q0 = (pair * 2 + (single > 0 ? 1 : 0)) * kTileM;
+  // Q tiles of this CTA that hold real rows
+  const int nt = (single < 0 && q0 + kTileM < a.Nq) ? 2 : 1;
 
   int kv_end = a.Nk;
   if (a.causal) {
-    const int last_row = min(q0 + 2 * kTileM - 1, a.Nq - 1);
+    const int last_row = min(q0 + nt * kTileM - 1, a.Nq - 1);
     const long long vis = a.q_pos0 + last_row - a.k_pos0 + 1;
     kv_end = static_cast<int>(max(0ll, min(static_cast<long long>(a.Nk), vis)));
   }
@@ -203,7 +214,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       float sq_t = 0.f, sk_next = 0.f;
       const float* sk_row = nullptr;
       if constexpr (QK8) {
-        sq_t = __ldg(a.sq + (static_cast<long long>(b) * a.Hq + h) * a.n_q_tiles + (pair * 2 + t));
+        sq_t = __ldg(a.sq + (static_cast<long long>(b) * a.Hq + h) * a.n_q_tiles + (q0 / kTileM + t));
         sk_row = a.sk + (static_cast<long long>(b) * a.Hkv + hk) * ((a.Nk + kTileN - 1) / kTileN);
         if (n_tiles > 0) sk_next = __ldg(sk_row);
       }
@@ -529,7 +540,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 // ---------------------------------------------------------------------------------
 template <int D, bool BF16, bool QK8>
-static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, cudaStream_t st) {
+static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_count, cudaStream_t st) {
   using L = WsLayout<D>;
   auto kern = fwd_ws_kernel<D, BF16, QK8>;
   cudaError_t e =
@@ -538,28 +549,41 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, cudaStre
   const long long n_pairs = (a.n_q_tiles + 1) / 2;
   const long long items = n_pairs * a.Hq * a.B;
   if (items > 0x7fffffffll) return cudaErrorInvalidValue;
-  kern<<<static_cast<unsigned>(items), kNumThreads, L::kDynSmem, st>>>(tm[0], tm[1], tm[2], tm[3],
-                                                                       a);
+  // One CTA per SM: `items` CTAs run in ceil(items / SMs) waves.  When the last wave would be at
+  // most half full, its pairs are split into single-tile CTAs (twice as many, each shorter), which
+  // still fit one wave; needs every tile to be real (even tile count) and enough K/V tiles to
+  // amortise a CTA.
+  FwdArgs args = a;
+  args.n_pair_items = static_cast<int>(items);
+  long long grid = items;
+  const long long rest = sm_count > 0 ? items % sm_count : 0;
+  const long long kv_tiles = (a.Nk + kTileN - 1) / kTileN;
+  static const bool no_split = getenv("MINIATTN_NO_TAIL_SPLIT") != nullptr;  // A/B switch for measurements
+  if (!no_split && items > sm_count && rest > 0 && 2 * rest <= sm_count && (a.n_q_tiles % 2) == 0 && kv_tiles >= 8) {
+    args.n_pair_items = static_cast<int>(items - rest);
+    grid = items + rest;
+  }
+  kern<<<static_cast<unsigned>(grid), kNumThreads, L::kDynSmem, st>>>(tm[0], tm[1], tm[2], tm[3],
+                                                                      args);
   return cudaGetLastError();
 }
 
 cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
                           cudaStream_t st) {
-  (void)sm_count;
   if (D == 128)
-    return bf16 ? launch_ws_t<128, true, false>(tm, a, st) : launch_ws_t<128, false, false>(tm, a, st);
+    return bf16 ? launch_ws_t<128, true, false>(tm, a, sm_count, st) : launch_ws_t<128, false, false>(tm, a, sm_count, st);
   if (D == 64)
-    return bf16 ? launch_ws_t<64, true, false>(tm, a, st) : launch_ws_t<64, false, false>(tm, a, st);
+    return bf16 ? launch_ws_t<64, true, false>(tm, a, sm_count, st) : launch_ws_t<64, false, false>(tm, a, sm_count, st);
   return cudaErrorInvalidValue;
 }
 
 // tm[0], tm[1]: int8 Q / K maps (one box of D bytes x 128 rows); tm[2], tm[3]: 16-bit V / O maps.
 cudaError_t launch_fwd_ws_int8qk(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
-                                 cudaStream_t st) {
+                                 int sm_count, cudaStream_t st) {
   if (D == 128)
-    return bf16 ? launch_ws_t<128, true, true>(tm, a, st) : launch_ws_t<128, false, true>(tm, a, st);
+    return bf16 ? launch_ws_t<128, true, true>(tm, a, sm_count, st) : launch_ws_t<128, false, true>(tm, a, sm_count, st);
   if (D == 64)
-    return bf16 ? launch_ws_t<64, true, true>(tm, a, st) : launch_ws_t<64, false, true>(tm, a, st);
+    return bf16 ? launch_ws_t<64, true, true>(tm, a, sm_count, st) : launch_ws_t<64, false, true>(tm, a, sm_count, st);
   return cudaErrorInvalidValue;
 }
 
