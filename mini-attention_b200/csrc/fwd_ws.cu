@@ -89,6 +89,9 @@ template <int N>
 __device__ __forceinline__ void reg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+#ifndef MA_TRACE_SOFTMAX
+#define MA_TRACE_SOFTMAX 1
+#endif
 #ifdef MA_TRACE
 constexpr int kTraceMax = 2048;
 #define MA_STAMP(role, tag)                                                              \
@@ -231,12 +234,12 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int hb = 0; hb < 2; ++hb) {
           mbar_wait(bar(L::kBarSFull + 2 * t + hb), j & 1, wc, kErrWaitS);
           tc_fence_after();
-          if (r == 0) MA_STAMP(t, 1);
+          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 1);
           uint32_t s[2][32];
           tmem_ld32(tS + hb * kHalfN, s[0]);
           tmem_ld32(tS + hb * kHalfN + 32, s[1]);
           tmem_wait_ld();
-          if (r == 0) MA_STAMP(t, 2);
+          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 2);
           if constexpr (QK8) {
             // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding
             // the bit pattern of 1.5*2^23 and subtracting that value is exact.
@@ -278,7 +281,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
           alpha_smem[(2 * t + hb) * kTileM + r] = alpha;
           warp_arrive(bar(L::kBarAlpha + 2 * t + hb));
-          if (r == 0) MA_STAMP(t, 3);
+          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 3);
 
           const float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
           float psum0 = 0.f, psum1 = 0.f;
@@ -298,7 +301,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tmem_wait_st();
           tc_fence_before();
           warp_arrive(bar(L::kBarPReady + 2 * t + hb));
-          if (r == 0) MA_STAMP(t, 4);
+          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 4);
         }
       }
 
