@@ -1,7 +1,7 @@
 """Build the reference's own mma.sync FlashAttention-2 forward extension for sm_100, as an on-box
 GPU baseline.  TEST / MEASUREMENT INFRASTRUCTURE ONLY: nothing in the product imports the result.
 
-    python oracle/build_ref_kernel.py [/path/to/Mini-Attention]
+    python oracle/build_ref_kernel.py /path/to/Mini-Attention
 
 Sources are compiled where they lie in the reference checkout
 (kernels/flash_attn/cuda/sm_120/kernel/flash_attention.cu + include/, the newest kernel tree) with
@@ -52,5 +52,6 @@ def load_built():
 
 
 if __name__ == "__main__":
-    root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
-    print(build(root))
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python oracle/build_ref_kernel.py /path/to/Mini-Attention")
+    print(build(Path(sys.argv[1])))

@@ -174,5 +174,7 @@ def kernel_config_strings(ref_root: Path) -> None:
 
 
 if __name__ == "__main__":
-    kernel_config_strings(Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference"))
-    main(Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference"))
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/Mini-Attention")
+    kernel_config_strings(Path(sys.argv[1]))
+    main(Path(sys.argv[1]))
