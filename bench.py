@@ -234,6 +234,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--kernel", default="auto")
     ap.add_argument("--seq-len", type=int, default=0, help="override the workload's sequence length")
+    ap.add_argument("--no-balance", action="store_true",
+                    help="plain launch (one CTA per work item) instead of the balanced one, for A/B timings")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the one-shot timings of the smaller N")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
@@ -315,7 +317,8 @@ def main():
             ring_out[0] = par.ring_forward(q, k, v, causal=causal, rank=rank, world=world)
     else:
         def attend():
-            miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel)
+            miniattn.flash_attn_fwd(q, k, v, causal=causal, out=o, kernel=args.kernel,
+                                    balance=not args.no_balance)
 
     def step_device():
         attend()
@@ -381,7 +384,8 @@ def main():
             qs = torch.randn(B, Hq, n, D, device=dev, dtype=dt)
             ks, vs = torch.randn_like(qs), torch.randn_like(qs)
             os_ = torch.empty_like(qs)
-            fn = lambda: miniattn.flash_attn_fwd(qs, ks, vs, out=os_, kernel=args.kernel)  # noqa: E731
+            fn = lambda: miniattn.flash_attn_fwd(qs, ks, vs, out=os_, kernel=args.kernel,  # noqa: E731
+                                                 balance=not args.no_balance)
             for _ in range(3):
                 fn()
             torch.cuda.synchronize(dev)
@@ -411,6 +415,7 @@ def main():
             "config": {"workload": w["name"], "per_gpu": shard, "seq_len": N, "head_dim": D, "causal": causal,
                        "parallelism": (f"zig-zag ring over {world} GPU(s): NCCL send/recv of K/V pairs + LSE merge" if ring
                                        else f"batch x head shards over {world} GPU(s), no communication"),
+                       "launch": "plain" if args.no_balance else "balanced (key ranges cut to fill the last round of CTAs)",
                        "l2": "flushed between steps (256 MiB write outside the timed intervals)",
                        "timing": "sum of per-step CUDA-event intervals on the launch stream, max over ranks"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",

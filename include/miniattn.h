@@ -18,6 +18,7 @@
 #ifndef MINIATTN_H_
 #define MINIATTN_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -77,6 +78,56 @@ typedef struct MiniAttnFwdParams {
 
 /* Launch the forward kernel on `stream` (a cudaStream_t; NULL = default stream). */
 int miniattn_fwd(const MiniAttnFwdParams* p, void* stream);
+
+/*
+ * Balanced forward launch (no counterpart in the reference, which launches one CTA per (batch,
+ * head, Q block) and leaves the balance to the hardware, flash_attention.cu:100-123).
+ *
+ * The kernel runs one CTA per SM, so a launch whose work items do not fill a whole number of
+ * rounds leaves SMs idle in the last one (256 items on 148 SMs: 2 rounds for 1.73 rounds of
+ * work).  This entry point plans the launch on the host: the key range of some items is cut into
+ * pieces that separate CTAs work on; the CTAs of a cut item leave un-normalised partial results
+ * in `scratch`, count themselves in on an arrival counter, and the last one to arrive folds the
+ * partials together and writes the output.  No CTA waits for another.  When the plan predicts no
+ * gain (many rounds, or too little work per item) the launch is the plain one and scratch is not
+ * touched.  Results equal miniattn_fwd's up to fp32 summation order.
+ *
+ * scratch: device memory, 256-byte aligned, at least miniattn_fwd_balanced_scratch_bytes(p)
+ * bytes.  Its first 8192 bytes (the arrival counters) must be zero before the first launch that
+ * uses it; every launch leaves them zero again, unless a bounded device wait ran out (status
+ * word != 0) — clear them before the next launch in that case.  Launches that may overlap on
+ * the GPU need separate scratch buffers.  scratch == NULL selects the plain launch.
+ */
+int miniattn_fwd_balanced(const MiniAttnFwdParams* p, void* scratch, size_t scratch_bytes, void* stream);
+
+/* Bytes of scratch the balanced launch of `p` needs on the current device (0: it would run the
+ * plain launch); a negative MINIATTN_E* code on error. */
+int64_t miniattn_fwd_balanced_scratch_bytes(const MiniAttnFwdParams* p);
+
+/* The plan itself, for inspection and tests: host arithmetic only, no device call when
+ * sm_count > 0 (sm_count <= 0 asks the current device).  Pointers in `p` are not read. */
+typedef struct MiniAttnPlanInfo {
+  int32_t split;         /* 1: some items are cut; 0: plain launch                              */
+  int32_t sm_count;
+  int64_t n_ctas;        /* CTAs of the launch                                                  */
+  int32_t n_whole;       /* CTAs [0, n_whole) take items [0, n_whole) whole                     */
+  int32_t n_pieces;      /* CTAs after them, described by `pieces`, longest first               */
+  int32_t n_cut_items;   /* items covered by more than one CTA                                  */
+  int32_t n_slots;       /* partial-result slots in scratch                                     */
+  int64_t scratch_bytes;
+  float est_plain;       /* predicted makespans in K/V-tile steps (128 keys) of one CTA         */
+  float est_balanced;
+} MiniAttnPlanInfo;
+
+typedef struct MiniAttnPlanPiece {
+  int32_t item;          /* index in launch order: Q-tile pair n_pairs-1 - item/(B*Hq), heads fastest */
+  int32_t t0, t1;        /* K/V tiles [t0, t1) of the item                                      */
+  int32_t part, nparts;  /* nparts == 1: the whole item                                         */
+  int32_t slot;          /* partial slot of a piece of a cut item, -1 otherwise                 */
+} MiniAttnPlanPiece;
+
+int miniattn_plan_fwd(const MiniAttnFwdParams* p, int sm_count, MiniAttnPlanInfo* info,
+                      MiniAttnPlanPiece* pieces, int32_t cap);
 
 /*
  * INT8-QK variant (SageAttention-style; the reference holds no code for it, only its task

@@ -16,7 +16,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "miniattn" / "libminiattn.so"
-SOURCES = ["api.cu", "fwd_simple.cu", "fwd_ws.cu", "merge.cu", "quant.cu", "selftest.cu"]
+SOURCES = ["api.cu", "fwd_simple.cu", "fwd_ws.cu", "merge.cu", "plan.cu", "quant.cu", "selftest.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",

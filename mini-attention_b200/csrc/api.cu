@@ -9,7 +9,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <mutex>
+#include <vector>
 
 #include "../../include/miniattn.h"
 #include "common.cuh"
@@ -21,6 +23,9 @@ cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs
                           cudaStream_t st);
 cudaError_t launch_fwd_ws_int8qk(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
                                  int sm_count, cudaStream_t st);
+cudaError_t launch_fwd_ws_plan(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
+                               const FwdPlan& plan, cudaStream_t st);
+void plan_fwd(const FwdArgs& a, int D, int sms, FwdPlan* plan);
 cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs, const void* k,
                             const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk, float q_fold,
                             int8_t* q8, int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
@@ -188,6 +193,9 @@ static void fill_args(const MiniAttnFwdParams* p, ma::FwdArgs* a) {
   a->sq = nullptr;
   a->sk = nullptr;
   a->trace = nullptr;
+  a->part_o = nullptr;
+  a->part_ml = nullptr;
+  a->counters = nullptr;
 #ifdef MA_TRACE
   a->trace = g_trace;
 #endif
@@ -203,7 +211,51 @@ static int check_device(int* sms) {
   return MINIATTN_OK;
 }
 
-int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
+// Plans of recent shapes (planning costs up to a millisecond of host time; launches of one shape
+// repeat).  Guarded by a mutex; an entry is copied out under the lock.
+namespace {
+struct PlanKey {
+  int Nq, Nk, B, Hq, causal, D, sms;
+  long long diag;
+  bool operator==(const PlanKey& o) const {
+    return Nq == o.Nq && Nk == o.Nk && B == o.B && Hq == o.Hq && causal == o.causal && D == o.D &&
+           sms == o.sms && diag == o.diag;
+  }
+};
+struct PlanSlot {
+  PlanKey key;
+  std::shared_ptr<const ma::FwdPlan> plan;
+};
+std::shared_ptr<const ma::FwdPlan> cached_plan(const ma::FwdArgs& a, int D, int sms) {
+  static std::mutex mu;
+  static std::vector<PlanSlot> cache;
+  static size_t next = 0;
+  const PlanKey key{a.Nq, a.Nk, a.B, a.Hq, a.causal, D, sms, a.causal ? a.q_pos0 - a.k_pos0 : 0};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    for (const PlanSlot& s : cache)
+      if (s.key == key) return s.plan;
+  }
+  auto plan = std::make_shared<ma::FwdPlan>();
+  ma::plan_fwd(a, D, sms, plan.get());
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() < 16) cache.push_back(PlanSlot{key, plan});
+  else cache[next++ % 16] = PlanSlot{key, plan};
+  return plan;
+}
+
+constexpr size_t kCounterBytes = 8192;  // 2 * kPlanCap arrival counters, rounded up
+static_assert(2 * ma::kPlanCap * sizeof(int) <= kCounterBytes, "counter region too small");
+size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+size_t scratch_bytes_of(const ma::FwdPlan& plan, int D) {
+  if (!plan.split) return 0;
+  const size_t rows = static_cast<size_t>(plan.n_slots) * 2 * ma::kTileM;
+  return kCounterBytes + align256(rows * sizeof(float2)) + rows * D * sizeof(float);
+}
+}  // namespace
+
+// Forward launch shared by miniattn_fwd and miniattn_fwd_balanced (scratch == nullptr: plain).
+static int fwd_common(const MiniAttnFwdParams* p, void* scratch, size_t scratch_bytes, void* stream) {
   g_err[0] = 0;
   int rc = check_fwd_params(p);
   if (rc != 0) return rc > 0 ? MINIATTN_OK : rc;
@@ -239,13 +291,96 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) {
   int kernel = p->kernel;
   if (kernel == MINIATTN_KERNEL_AUTO) kernel = MINIATTN_KERNEL_WS;
   cudaError_t e;
-  if (kernel == MINIATTN_KERNEL_SIMPLE)
+  if (kernel == MINIATTN_KERNEL_SIMPLE) {
     e = ma::launch_fwd_simple(p->D, p->dtype == MINIATTN_BF16, tm, a, st);
-  else
-    e = ma::launch_fwd_ws(p->D, p->dtype == MINIATTN_BF16, tm, a, sms, st);
+  } else {
+    std::shared_ptr<const ma::FwdPlan> plan;
+    if (scratch != nullptr && has_keys) plan = cached_plan(a, p->D, sms);
+    if (plan && plan->split) {
+      const size_t need = scratch_bytes_of(*plan, p->D);
+      if (scratch_bytes < need)
+        return fail(MINIATTN_EINVAL, "scratch holds %zu bytes, this launch needs %zu "
+                    "(miniattn_fwd_balanced_scratch_bytes)", scratch_bytes, need);
+      if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0)
+        return fail(MINIATTN_EINVAL, "scratch must be 256-byte aligned");
+      uint8_t* base = static_cast<uint8_t*>(scratch);
+      const size_t rows = static_cast<size_t>(plan->n_slots) * 2 * ma::kTileM;
+      a.counters = reinterpret_cast<int*>(base);
+      a.part_ml = reinterpret_cast<float2*>(base + kCounterBytes);
+      a.part_o = reinterpret_cast<float*>(base + kCounterBytes + align256(rows * sizeof(float2)));
+      e = ma::launch_fwd_ws_plan(p->D, p->dtype == MINIATTN_BF16, tm, a, *plan, st);
+    } else {
+      e = ma::launch_fwd_ws(p->D, p->dtype == MINIATTN_BF16, tm, a, sms, st);
+    }
+  }
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;
+}
+
+int miniattn_fwd(const MiniAttnFwdParams* p, void* stream) { return fwd_common(p, nullptr, 0, stream); }
+
+int miniattn_fwd_balanced(const MiniAttnFwdParams* p, void* scratch, size_t scratch_bytes, void* stream) {
+  if (scratch == nullptr && scratch_bytes != 0) {
+    g_err[0] = 0;
+    return fail(MINIATTN_EINVAL, "scratch is null but scratch_bytes is %zu", scratch_bytes);
+  }
+  return fwd_common(p, scratch, scratch_bytes, stream);
+}
+
+// Plan of a forward launch for `sm_count` SMs (<= 0: the current device's).  Host arithmetic only.
+int miniattn_plan_fwd(const MiniAttnFwdParams* p, int sm_count, MiniAttnPlanInfo* info,
+                      MiniAttnPlanPiece* pieces, int32_t cap) {
+  g_err[0] = 0;
+  if (info == nullptr) return fail(MINIATTN_EINVAL, "info is null");
+  memset(info, 0, sizeof(*info));
+  if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
+  if (p->D != 64 && p->D != 128)
+    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64 or 128)", p->D);
+  if (p->B < 0 || p->Hq < 0 || p->Nq < 0 || p->Nk < 0) return fail(MINIATTN_EINVAL, "negative size");
+  if (p->Hq > 65535 || p->B > 65535)
+    return fail(MINIATTN_EUNSUPPORTED, "B and Hq must not exceed 65535");
+  int sms = sm_count;
+  if (sms <= 0) {
+    int rc;
+    if ((rc = check_device(&sms)) != 0) return rc;
+  }
+  ma::FwdArgs a;
+  fill_args(p, &a);
+  const long long n_items = static_cast<long long>((a.n_q_tiles + 1) / 2) * p->Hq * p->B;
+  info->sm_count = sms;
+  info->n_ctas = n_items;
+  if (p->B == 0 || p->Hq == 0 || p->Nq == 0 || p->Nk == 0 ||
+      (p->kernel != MINIATTN_KERNEL_AUTO && p->kernel != MINIATTN_KERNEL_WS))
+    return MINIATTN_OK;
+  std::shared_ptr<const ma::FwdPlan> plan = cached_plan(a, p->D, sms);
+  info->est_plain = plan->est_plain;
+  info->est_balanced = plan->est_balanced;
+  if (!plan->split) return MINIATTN_OK;
+  info->split = 1;
+  info->n_whole = plan->n_whole;
+  info->n_pieces = plan->n_table;
+  info->n_ctas = plan->n_whole + plan->n_table;
+  info->n_cut_items = plan->n_cut_items;
+  info->n_slots = plan->n_slots;
+  info->scratch_bytes = static_cast<int64_t>(scratch_bytes_of(*plan, p->D));
+  if (pieces != nullptr)
+    for (int k = 0; k < plan->n_table && k < cap; ++k) {
+      const ma::PlanEntry& e = plan->table.e[k];
+      pieces[k].item = static_cast<int32_t>(e.item);
+      pieces[k].t0 = e.t0;
+      pieces[k].t1 = e.t1;
+      pieces[k].part = e.part;
+      pieces[k].nparts = e.nparts;
+      pieces[k].slot = e.nparts > 1 ? e.slot0 + e.part : -1;
+    }
+  return MINIATTN_OK;
+}
+
+int64_t miniattn_fwd_balanced_scratch_bytes(const MiniAttnFwdParams* p) {
+  MiniAttnPlanInfo info;
+  const int rc = miniattn_plan_fwd(p, 0, &info, nullptr, 0);
+  return rc != 0 ? rc : info.scratch_bytes;
 }
 
 static int check_int8_params(const MiniAttnInt8Params* p, bool need_v) {

@@ -2,6 +2,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda.h>
+#include <vector_types.h>
 
 namespace ma {
 
@@ -20,11 +21,54 @@ struct FwdArgs {
   const float* sq;     // INT8-QK: [B, Hq,  ceil(Nq/128)] Q scales (softmax scale * log2e folded in)
   const float* sk;     // INT8-QK: [B, Hkv, ceil(Nk/128)] K scales
   unsigned long long* trace;  // debug builds only (MA_TRACE): per-role clock stamps of CTA 0
+  // Balanced launches only (null otherwise): where CTAs that cover part of an item's key range
+  // leave their partial result, and the per-item arrival counters (zero between launches).
+  float*  part_o;      // [slot][2 tiles][D/4][128 rows][4] fp32, un-normalised O of a piece
+  float2* part_ml;     // [slot][2 tiles][128 rows]: (row maximum in log2 units, row sum)
+  int*    counters;    // [cut item][2 tiles]
+};
+
+// One CTA of a balanced launch, read from the launch's table (kernel parameter space).
+struct PlanEntry {
+  uint32_t item;         // index in the heaviest-first item order
+  uint16_t t0, t1;       // the CTA covers K/V tiles [t0, t1) of the item
+  uint16_t slot0;        // first partial slot of the item (its pieces hold consecutive slots)
+  uint8_t  part, nparts; // nparts == 1: whole item, the CTA writes the output itself
+  uint32_t counter;      // arrival-counter index of a cut item
+};
+constexpr int kPlanCap = 768;
+struct PlanTable { PlanEntry e[kPlanCap]; };
+struct NoPlanTable { int unused; };
+
+// Result of the host-side planner (plan.cu).
+struct FwdPlan {
+  bool split;            // false: launch the items as they are
+  int n_whole;           // CTAs [0, n_whole) take items [0, n_whole) whole
+  int n_table;           // the CTAs after them read table.e[cta - n_whole]
+  int n_slots;           // partial slots the launch writes
+  int n_cut_items;       // items covered by more than one CTA
+  float est_plain;       // predicted makespans, in K/V-tile steps of one CTA
+  float est_balanced;
+  PlanTable table;
 };
 
 constexpr int kTileM = 128;   // query rows per MMA tile (TMEM lanes)
 constexpr int kTileN = 128;   // keys per K/V tile
 constexpr int kBoxCols = 64;  // 16-bit elements per 128-byte swizzled row
 constexpr int kBoxBytes = kTileN * 128;  // one [128 rows x 128 B] TMA box
+
+// Number of K/V tiles the Q rows [q0, q0 + nt*128) have to visit (all of them without a mask,
+// up to the diagonal of the last row with one).  Shared by the kernels and the host planner.
+__host__ __device__ inline int kv_tiles_of(const FwdArgs& a, int q0, int nt) {
+  long long kv_end = a.Nk;
+  if (a.causal) {
+    long long last_row = q0 + nt * kTileM - 1;
+    if (last_row > a.Nq - 1) last_row = a.Nq - 1;
+    long long vis = a.q_pos0 + last_row - a.k_pos0 + 1;
+    if (vis < kv_end) kv_end = vis;
+    if (kv_end < 0) kv_end = 0;
+  }
+  return static_cast<int>((kv_end + kTileN - 1) / kTileN);
+}
 
 }  // namespace ma

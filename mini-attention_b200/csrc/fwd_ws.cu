@@ -29,6 +29,7 @@
 // true maximum has grown by more than 2^8 (in the exp2 domain), so the O accumulator is rescaled
 // only rarely; l is accumulated against the same maximum, which keeps O / l exact.
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -69,8 +70,8 @@ struct WsLayout {
   static constexpr int kBarODone = kBarOReady + 4;         // [2][2] MMA -> correction
   static constexpr int kBarLReady = kBarODone + 4;         // [2]    softmax -> correction (final l)
   static constexpr int kNumBars = kBarLReady + 2;
-  static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem slot, abort flag
-  static constexpr int kBytes = kOffMisc + 16;
+  static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem slot, abort flag, arrival order [2]
+  static constexpr int kBytes = kOffMisc + 32;
   static constexpr int kDynSmem = kBytes + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0;     // S buffer of (tile t, half h) at kColS + 128*t + 64*h
@@ -92,11 +93,14 @@ __device__ __forceinline__ void reg_dec() {
 #ifndef MA_TRACE_SOFTMAX
 #define MA_TRACE_SOFTMAX 1
 #endif
+#ifndef MA_TRACE_CTA
+#define MA_TRACE_CTA 0
+#endif
 #ifdef MA_TRACE
 constexpr int kTraceMax = 2048;
 #define MA_STAMP(role, tag)                                                              \
   do {                                                                                   \
-    if (a.trace != nullptr && blockIdx.x == 0 && trace_n < kTraceMax)                    \
+    if (a.trace != nullptr && blockIdx.x == MA_TRACE_CTA && trace_n < kTraceMax)         \
       a.trace[(role) * kTraceMax + trace_n++] =                                          \
           (static_cast<unsigned long long>(tag) << 48) | (clock64() & 0xFFFFFFFFFFFFull); \
   } while (0)
@@ -113,11 +117,18 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar) {
 // QK8: Q and K arrive as int8 (one fp32 scale per 128-token block, softmax scale * log2e folded
 // into the Q scales); S = Q8 K8^T runs on tcgen05 kind::i8 with an int32 accumulator and is
 // de-quantised on the fly in the softmax; P, V and the PV MMA stay 16 bit.
-template <int D, bool BF16, bool QK8>
+//
+// PLAN: balanced launch.  CTAs past the first a.n_pair_items read their work from `plan`: an item
+// and a range of its K/V tiles.  The CTAs that share an item each leave their un-normalised O and
+// (row maximum, row sum) in scratch memory, count themselves in on the item's arrival counter, and
+// the one that arrives last folds the others' partials into its own and writes the output; nobody
+// waits for another CTA.
+template <int D, bool BF16, bool QK8, bool PLAN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-              const FwdArgs a) {
+              const FwdArgs a,
+              const __grid_constant__ std::conditional_t<PLAN, PlanTable, NoPlanTable> plan) {
   using L = WsLayout<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -131,7 +142,13 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   auto bar = [&](int idx) -> uint32_t { return bars + 8u * idx; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kOffMisc + 8);
+  volatile int* arrival = reinterpret_cast<volatile int*>(gbase + L::kOffMisc + 16);  // [2 tiles]
 
+#ifdef MA_TRACE
+  const long long trace_entry = clock64();
+  // per-CTA record after the stamp area: (SM id, global timer at entry, at exit)
+  const unsigned long long trace_t0 = global_timer_ns();
+#endif
   const int tid = threadIdx.x;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler
   const int lane = tid & 31;
@@ -143,10 +160,22 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int bh_total = a.Hq * a.B;
   int item = blockIdx.x;
   int single = -1;  // which tile of its pair a single-tile CTA takes
+  int pe_t0 = 0, pe_t1 = -1, pe_part = 0, pe_nparts = 1, pe_slot0 = 0, pe_counter = 0;
   if (item >= a.n_pair_items) {
-    const int s_idx = item - a.n_pair_items;
-    item = a.n_pair_items + (s_idx >> 1);
-    single = s_idx & 1;
+    if constexpr (PLAN) {
+      const PlanEntry& e = plan.e[item - a.n_pair_items];
+      item = static_cast<int>(e.item);
+      pe_t0 = e.t0;
+      pe_t1 = e.t1;
+      pe_part = e.part;
+      pe_nparts = e.nparts;
+      pe_slot0 = e.slot0;
+      pe_counter = static_cast<int>(e.counter);
+    } else {
+      const int s_idx = item - a.n_pair_items;
+      item = a.n_pair_items + (s_idx >> 1);
+      single = s_idx & 1;
+    }
   }
   const int pair = n_pairs - 1 - item / bh_total;
   const int bh = item % bh_total;
@@ -157,13 +186,19 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   // Q tiles of this CTA that hold real rows
   const int nt = (single < 0 && q0 + kTileM < a.Nq) ? 2 : 1;
 
+  // K/V tiles [kv_t0, kv_t0 + n_tiles) of this CTA: all the rows can see, or the table's range
   int kv_end = a.Nk;
   if (a.causal) {
     const int last_row = min(q0 + nt * kTileM - 1, a.Nq - 1);
     const long long vis = a.q_pos0 + last_row - a.k_pos0 + 1;
     kv_end = static_cast<int>(max(0ll, min(static_cast<long long>(a.Nk), vis)));
   }
-  const int n_tiles = (kv_end + kTileN - 1) / kTileN;
+  int kv_t0 = 0;
+  int n_tiles = (kv_end + kTileN - 1) / kTileN;  // == kv_tiles_of(a, q0, nt)
+  if (PLAN && pe_t1 >= 0) {
+    kv_t0 = pe_t0;
+    n_tiles = pe_t1 - pe_t0;
+  }
 
   if (warp == 13 && lane == 0) {
     mbar_init(bar(L::kBarQFull + 0), 1);
@@ -207,6 +242,11 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (t < nt) {
       const int r = tid & 127;
       const int row = q0 + t * kTileM + r;
+#ifdef MA_TRACE
+      if (r == 0 && a.trace != nullptr && blockIdx.x == MA_TRACE_CTA)
+        a.trace[t * kTraceMax + trace_n++] = (18ull << 48) | (trace_entry & 0xFFFFFFFFFFFFull);
+#endif
+      if (r == 0) MA_STAMP(t, 19);
       const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
       const uint32_t tS = tmem_base + L::kColS + 128 * t + lane_off;
       long long vis_ll = a.Nk;
@@ -219,6 +259,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if constexpr (QK8) {
         sq_t = __ldg(a.sq + (static_cast<long long>(b) * a.Hq + h) * a.n_q_tiles + (q0 / kTileM + t));
         sk_row = a.sk + (static_cast<long long>(b) * a.Hkv + hk) * ((a.Nk + kTileN - 1) / kTileN);
+        sk_row += kv_t0;
         if (n_tiles > 0) sk_next = __ldg(sk_row);
       }
 
@@ -249,7 +290,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               for (int i = 0; i < 32; ++i)
                 s[q][i] = __float_as_uint(__uint_as_float(s[q][i] + 0x4B400000u) - 12582912.f);
           }
-          const int lim = vis_row - j * kTileN - hb * kHalfN;
+          const int lim = vis_row - (kv_t0 + j) * kTileN - hb * kHalfN;
           if (lim < kHalfN) {  // diagonal or ragged half: hide the keys this row must not see
 #pragma unroll
             for (int q = 0; q < 2; ++q)
@@ -305,56 +346,184 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
 
-      if (a.lse != nullptr && row < a.Nq) {
+      if ((!PLAN || pe_nparts == 1) && a.lse != nullptr && row < a.Nq) {
         const float lse = (l_run > 0.f) ? (m_cur * 0.6931471805599453f + __logf(l_run)) : -INFINITY;
         a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] = lse;
       }
-      // ---- epilogue of this Q tile (the two softmax groups run theirs side by side):
-      //      O / l -> 16 bit -> swizzled smem (the tile's Q buffer) -> TMA store
-      const float inv_l = (l_run > 0.f) ? (1.f / l_run) : 0.f;
+      const uint32_t tO = tmem_base + L::kColO + D * t + lane_off;
       if (n_tiles > 0) {
         mbar_wait(bar(L::kBarODone + 2 * t + 1), (n_tiles - 1) & 1, wc, kErrWaitO);
         tc_fence_after();
       }
-      const uint32_t tO = tmem_base + L::kColO + D * t + lane_off;
-      const uint32_t stage = sQ + t * L::kTileBytes;
+      if (r == 0) MA_STAMP(t, 20);
+      // A CTA that covers a piece of an item's key range publishes its partial result; the last
+      // piece to arrive folds the other pieces into its own accumulator and writes the output.
+      float f_self = (l_run > 0.f) ? (1.f / l_run) : 0.f;  // factor of this CTA's own accumulator
+      float f_part = 0.f;            // factor of the partial waiting in shared memory (if any)
+      const float4* s_part = nullptr; // that partial: [D/4][128 rows][4] fp32, offset to this row
+      bool write_out = true;
+      if constexpr (PLAN) {
+        if (pe_nparts > 1) {
+          // un-normalised O as [D/4][128 rows][4] fp32 (a warp writes 512 contiguous bytes per
+          // store), and (m, l) of every row
+          const long long my = (static_cast<long long>(pe_slot0 + pe_part) * 2 + t) * kTileM;
+          float4* po = reinterpret_cast<float4*>(a.part_o + my * D) + r;
 #pragma unroll
-      for (int q = 0; q < D / 32; ++q) {
-        uint32_t o[32];
-        if (n_tiles > 0) {
-          tmem_ld32(tO + q * 32, o);
-          tmem_wait_ld();
-        } else {
+          for (int q = 0; q < D / 32; ++q) {
+            uint32_t o[32];
+            tmem_ld32(tO + q * 32, o);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
+            for (int g = 0; g < 8; ++g)
+              po[(q * 8 + g) * kTileM] =
+                  make_float4(__uint_as_float(o[4 * g]), __uint_as_float(o[4 * g + 1]),
+                              __uint_as_float(o[4 * g + 2]), __uint_as_float(o[4 * g + 3]));
+          }
+          a.part_ml[my + r] = make_float2(m_cur, l_run);
+          if (r == 0) MA_STAMP(t, 21);
+          __threadfence();
+          named_bar_sync(kBarEpilogue + t, 128);
+          if (r == 0) MA_STAMP(t, 22);
+          if (r == 0) arrival[t] = atomicAdd(a.counters + 2 * pe_counter + t, 1);
+          named_bar_sync(kBarEpilogue + t, 128);
+          if (r == 0) MA_STAMP(t, 23);
+          write_out = (arrival[t] == pe_nparts - 1);
+          if (write_out) {
+            if (r == 0) a.counters[2 * pe_counter + t] = 0;  // leave the counter as it was found
+            __threadfence();
+            // The other pieces' partials come in through the K/V ring (this tile's half of it),
+            // one bulk copy each; the ring is free once the other Q tile's MMAs are done too.
+            // The first copy is started before anything else so that the rest overlaps it.
+            if (nt == 2) mbar_wait(bar(L::kBarODone + 2 * (1 - t) + 1), (n_tiles - 1) & 1, wc, kErrWaitO);
+            constexpr uint32_t kPartBytes = D * kTileM * 4;
+            const uint32_t ring_off = L::kOffRing + t * (L::kStages / 2) * L::kTileBytes;
+            const int first_other = (pe_part == 0) ? 1 : 0;
+            const int last_other = (pe_part == pe_nparts - 1) ? pe_nparts - 2 : pe_nparts - 1;
+            auto fetch = [&](int p) {
+              mbar_expect_tx(bar(L::kBarQFull + t), kPartBytes);
+              bulk_load(sbase + ring_off, a.part_o + (static_cast<long long>(pe_slot0 + p) * 2 + t) * kTileM * D,
+                        kPartBytes, bar(L::kBarQFull + t));
+            };
+            if (r == 0) {
+              fence_proxy_async_all();
+              fetch(first_other);
+            }
+            // totals of the row over all pieces, one pass (the same running-maximum rule)
+            const float2* ml0 = a.part_ml + (static_cast<long long>(pe_slot0) * 2 + t) * kTileM + r;
+            float m_tot = m_cur, l_tot = l_run, m_first = -INFINITY;
+#pragma unroll 4
+            for (int p = 0; p < pe_nparts; ++p) {
+              if (p == pe_part) continue;
+              const float2 ml = __ldcg(ml0 + static_cast<long long>(p) * 2 * kTileM);
+              if (p == first_other) m_first = ml.x;
+              const float m_new = fmaxf(m_tot, ml.x);
+              const float mn = (m_new == -INFINITY) ? 0.f : m_new;
+              l_tot = l_tot * ex2(m_tot - mn) + ml.y * ex2(ml.x - mn);
+              m_tot = m_new;
+            }
+            const float mt = (m_tot == -INFINITY) ? 0.f : m_tot;
+            const float inv_l = (l_tot > 0.f) ? (1.f / l_tot) : 0.f;
+            if (r == 0) MA_STAMP(t, 24);
+            if (a.lse != nullptr && row < a.Nq)
+              a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] =
+                  (l_tot > 0.f) ? (m_tot * 0.6931471805599453f + __logf(l_tot)) : -INFINITY;
+            s_part = reinterpret_cast<const float4*>(gbase + ring_off) + r;
+            uint32_t phase = 1;  // the Q barrier of this tile completed its phase 0 with the Q load
+            bool own_scaled = false;
+            const float w_self = ex2(m_cur - mt);
+            for (int p = 0; p < pe_nparts; ++p) {
+              if (p == pe_part) continue;
+              if (p != first_other && r == 0) fetch(p);
+              const float m_p = (p == first_other) ? m_first : __ldcg(ml0 + static_cast<long long>(p) * 2 * kTileM).x;
+              const float wp = ex2(m_p - mt);
+              mbar_wait(bar(L::kBarQFull + t), phase, wc, kErrWaitKV);
+              phase ^= 1;
+              if (r == 0) MA_STAMP(t, 25);
+              if (p == last_other) {  // folded in while the output is written, below
+                f_part = wp * inv_l;
+                break;
+              }
+              // more than two pieces: accumulate into the TMEM accumulator
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int col = q * 32 + ch * 8;
-          const int bx = col >> 6;
-          const int chunk = (col & 63) >> 3;
-          const uint32_t addr = stage + bx * kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
-          const uint32_t w0 = pack2<BF16>(__uint_as_float(o[ch * 8 + 0]) * inv_l,
-                                          __uint_as_float(o[ch * 8 + 1]) * inv_l);
-          const uint32_t w1 = pack2<BF16>(__uint_as_float(o[ch * 8 + 2]) * inv_l,
-                                          __uint_as_float(o[ch * 8 + 3]) * inv_l);
-          const uint32_t w2 = pack2<BF16>(__uint_as_float(o[ch * 8 + 4]) * inv_l,
-                                          __uint_as_float(o[ch * 8 + 5]) * inv_l);
-          const uint32_t w3 = pack2<BF16>(__uint_as_float(o[ch * 8 + 6]) * inv_l,
-                                          __uint_as_float(o[ch * 8 + 7]) * inv_l);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
-                       "r"(w2), "r"(w3)
-                       : "memory");
+              for (int q = 0; q < D / 32; ++q) {
+                uint32_t o[32];
+                tmem_ld32(tO + q * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  const float4 x = s_part[(q * 8 + g) * kTileM];
+                  const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float own = own_scaled ? __uint_as_float(o[4 * g + e]) : __uint_as_float(o[4 * g + e]) * w_self;
+                    o[4 * g + e] = __float_as_uint(fmaf(xs[e], wp, own));
+                  }
+                }
+                tmem_st32(tO + q * 32, o);
+              }
+              tmem_wait_st();
+              own_scaled = true;
+              named_bar_sync(kBarEpilogue + t, 128);  // everyone has read the partial: the next may land
+            }
+            f_self = own_scaled ? inv_l : w_self * inv_l;
+          }
         }
       }
-      fence_proxy_async_smem();
-      named_bar_sync(kBarEpilogue + t, 128);
-      if (r == 0) {
+      if (write_out) {
+        // ---- epilogue of this Q tile (the two softmax groups run theirs side by side):
+        //      O / l -> 16 bit -> swizzled smem (the tile's Q buffer) -> TMA store
+        const uint32_t stage = sQ + t * L::kTileBytes;
 #pragma unroll
-        for (int bx = 0; bx < L::kBoxes; ++bx)
-          tma_store_4d(&tm_o, stage + bx * kBoxBytes, bx * kBoxCols, q0 + t * kTileM, h, b);
-        tma_store_commit();
-        tma_store_wait_all();
+        for (int q = 0; q < D / 32; ++q) {
+          float o[32];
+          if (n_tiles > 0) {
+            uint32_t u[32];
+            tmem_ld32(tO + q * 32, u);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(u[i]) * f_self;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0.f;
+          }
+          if constexpr (PLAN) {
+            if (s_part != nullptr) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                const float4 x = s_part[(q * 8 + g) * kTileM];
+                o[4 * g + 0] = fmaf(x.x, f_part, o[4 * g + 0]);
+                o[4 * g + 1] = fmaf(x.y, f_part, o[4 * g + 1]);
+                o[4 * g + 2] = fmaf(x.z, f_part, o[4 * g + 2]);
+                o[4 * g + 3] = fmaf(x.w, f_part, o[4 * g + 3]);
+              }
+            }
+          }
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const int col = q * 32 + ch * 8;
+            const int bx = col >> 6;
+            const int chunk = (col & 63) >> 3;
+            const uint32_t addr = stage + bx * kBoxBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
+            const uint32_t w0 = pack2<BF16>(o[ch * 8 + 0], o[ch * 8 + 1]);
+            const uint32_t w1 = pack2<BF16>(o[ch * 8 + 2], o[ch * 8 + 3]);
+            const uint32_t w2 = pack2<BF16>(o[ch * 8 + 4], o[ch * 8 + 5]);
+            const uint32_t w3 = pack2<BF16>(o[ch * 8 + 6], o[ch * 8 + 7]);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
+                         "r"(w2), "r"(w3)
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(kBarEpilogue + t, 128);
+        if (r == 0) {
+          MA_STAMP(t, 26);
+#pragma unroll
+          for (int bx = 0; bx < L::kBoxes; ++bx)
+            tma_store_4d(&tm_o, stage + bx * kBoxBytes, bx * kBoxCols, q0 + t * kTileM, h, b);
+          tma_store_commit();
+          tma_store_wait_all();
+          MA_STAMP(t, 27);
+        }
       }
       tc_fence_before();
     }
@@ -508,7 +677,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const int use = i / L::kStages;
           if (use > 0) mbar_wait(bar(L::kBarKvEmpty + slot), (use - 1) & 1, wc, kErrWaitFree);
           const uint32_t fb = bar(L::kBarKvFull + slot);
-          const int j = i >> 1;
+          const int j = kv_t0 + (i >> 1);
           if (QK8 && !(i & 1)) {  // int8 K tile: one box of D bytes x 128 rows
             mbar_expect_tx(fb, kTileN * D);
             tma_load_4d(sRing + slot * L::kTileBytes, &tm_k, fb, 0, j * kTileN, hk, b);
@@ -539,13 +708,23 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem_base, L::kTmemCols);
   }
+#ifdef MA_TRACE
+  if (tid == 0 && a.trace != nullptr) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    unsigned long long* rec = a.trace + 5 * kTraceMax + 3ull * blockIdx.x;
+    rec[0] = smid;
+    rec[1] = trace_t0;
+    rec[2] = global_timer_ns();
+  }
+#endif
 }
 
 // ---------------------------------------------------------------------------------
 template <int D, bool BF16, bool QK8>
 static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_count, cudaStream_t st) {
   using L = WsLayout<D>;
-  auto kern = fwd_ws_kernel<D, BF16, QK8>;
+  auto kern = fwd_ws_kernel<D, BF16, QK8, false>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
   if (e != cudaSuccess) return e;
@@ -558,6 +737,9 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_c
   // amortise a CTA.
   FwdArgs args = a;
   args.n_pair_items = static_cast<int>(items);
+  args.part_o = nullptr;
+  args.part_ml = nullptr;
+  args.counters = nullptr;
   long long grid = items;
   const long long rest = sm_count > 0 ? items % sm_count : 0;
   const long long kv_tiles = (a.Nk + kTileN - 1) / kTileN;
@@ -567,8 +749,31 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_c
     grid = items + rest;
   }
   kern<<<static_cast<unsigned>(grid), kNumThreads, L::kDynSmem, st>>>(tm[0], tm[1], tm[2], tm[3],
-                                                                      args);
+                                                                      args, NoPlanTable{0});
   return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+static cudaError_t launch_plan_t(const CUtensorMap* tm, const FwdArgs& a, const FwdPlan& plan,
+                                 cudaStream_t st) {
+  using L = WsLayout<D>;
+  auto kern = fwd_ws_kernel<D, BF16, false, true>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
+  if (e != cudaSuccess) return e;
+  FwdArgs args = a;
+  args.n_pair_items = plan.n_whole;
+  const unsigned grid = static_cast<unsigned>(plan.n_whole + plan.n_table);
+  kern<<<grid, kNumThreads, L::kDynSmem, st>>>(tm[0], tm[1], tm[2], tm[3], args, plan.table);
+  return cudaGetLastError();
+}
+
+// Balanced launch: a.part_o / a.part_ml / a.counters point into the caller's scratch.
+cudaError_t launch_fwd_ws_plan(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
+                               const FwdPlan& plan, cudaStream_t st) {
+  if (D == 128) return bf16 ? launch_plan_t<128, true>(tm, a, plan, st) : launch_plan_t<128, false>(tm, a, plan, st);
+  if (D == 64) return bf16 ? launch_plan_t<64, true>(tm, a, plan, st) : launch_plan_t<64, false>(tm, a, plan, st);
+  return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,

@@ -62,6 +62,25 @@ class MergeSplitParams(C.Structure):
     ]
 
 
+class PlanInfo(C.Structure):
+    """Mirror of ``MiniAttnPlanInfo``."""
+
+    _fields_ = [
+        ("split", C.c_int32), ("sm_count", C.c_int32), ("n_ctas", C.c_int64),
+        ("n_whole", C.c_int32), ("n_pieces", C.c_int32), ("n_cut_items", C.c_int32), ("n_slots", C.c_int32),
+        ("scratch_bytes", C.c_int64), ("est_plain", C.c_float), ("est_balanced", C.c_float),
+    ]
+
+
+class PlanPiece(C.Structure):
+    """Mirror of ``MiniAttnPlanPiece``."""
+
+    _fields_ = [
+        ("item", C.c_int32), ("t0", C.c_int32), ("t1", C.c_int32),
+        ("part", C.c_int32), ("nparts", C.c_int32), ("slot", C.c_int32),
+    ]
+
+
 def _load() -> C.CDLL:
     if not _LIB_PATH.exists():
         raise ImportError(
@@ -71,6 +90,13 @@ def _load() -> C.CDLL:
     lib = C.CDLL(str(_LIB_PATH))
     lib.miniattn_fwd.argtypes = [C.POINTER(FwdParams), C.c_void_p]
     lib.miniattn_fwd.restype = C.c_int
+    lib.miniattn_fwd_balanced.argtypes = [C.POINTER(FwdParams), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.miniattn_fwd_balanced.restype = C.c_int
+    lib.miniattn_fwd_balanced_scratch_bytes.argtypes = [C.POINTER(FwdParams)]
+    lib.miniattn_fwd_balanced_scratch_bytes.restype = C.c_int64
+    lib.miniattn_plan_fwd.argtypes = [C.POINTER(FwdParams), C.c_int, C.POINTER(PlanInfo),
+                                      C.POINTER(PlanPiece), C.c_int32]
+    lib.miniattn_plan_fwd.restype = C.c_int
     for name in ("miniattn_quant_qk_int8", "miniattn_quant_qk_int8_static", "miniattn_fwd_int8qk"):
         getattr(lib, name).argtypes = [C.POINTER(Int8Params), C.c_void_p]
         getattr(lib, name).restype = C.c_int

@@ -18,6 +18,7 @@ from . import _lib
 
 _DTYPES = {torch.float16: _lib.FP16, torch.bfloat16: _lib.BF16}
 _status_words: dict = {}
+_balance_scratch: dict = {}   # (device index, stream) -> zero-initialised uint8 scratch tensor
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -38,7 +39,38 @@ def device_status(device: Union[torch.device, str, None] = None) -> int:
     val = int(t.item())
     if val:
         t.zero_()
+        # a launch that gave up may have left arrival counters of a balanced launch non-zero
+        for key in [k for k in _balance_scratch if k[0] == device.index]:
+            del _balance_scratch[key]
     return val
+
+
+def _scratch_for(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Scratch of a balanced launch: one buffer per (device, stream), zeroed when created (the
+    kernels leave the arrival counters at its start zero again), grown on demand."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    t = _balance_scratch.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _balance_scratch[key] = t
+    return t
+
+
+def plan_info(B: int, Hq: int, Nq: int, Nk: int, D: int = 128, *, causal: bool = False, q_pos0: int = 0,
+              k_pos0: int = 0, sm_count: int = 148):
+    """The launch plan of a forward call on a GPU with `sm_count` SMs (host arithmetic only, no
+    device needed): ``(info, pieces)`` with `info` a :class:`_lib.PlanInfo` and `pieces` the list
+    of (item, t0, t1, part, nparts, slot) of the CTAs that follow the whole-item prefix."""
+    p = _lib.FwdParams()
+    p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D = B, Hq, Hq, Nq, Nk, D
+    p.causal = 1 if causal else 0
+    p.q_pos0, p.k_pos0 = int(q_pos0), int(k_pos0)
+    info = _lib.PlanInfo()
+    cap = 1024
+    arr = (_lib.PlanPiece * cap)()
+    _lib.check(_lib.lib.miniattn_plan_fwd(C.byref(p), int(sm_count), C.byref(info), arr, cap), "miniattn_plan_fwd")
+    pieces = [(e.item, e.t0, e.t1, e.part, e.nparts, e.slot) for e in arr[: info.n_pieces]]
+    return info, pieces
 
 
 def _bhn_strides(t: torch.Tensor, layout: str) -> Tuple[int, int, int]:
@@ -122,7 +154,7 @@ def flash_attn_fwd(
     kernel: str = "auto",
     q_pos0: int = 0,
     k_pos0: int = 0,
-    split_tail: bool = False,
+    balance: bool = True,
 ):
     """O = softmax(Q K^T * scale [+ causal mask]) V on the GPU.
 
@@ -132,112 +164,26 @@ def flash_attn_fwd(
     kernels/standard/pytorch/gqa.py:38-39).  Causal: key j is visible to query i iff
     ``k_pos0 + j <= q_pos0 + i`` (kernels/flash_attn/triton/fp16_flash_attn_sm86.py:74-75
     with both offsets 0).  Returns ``out`` or ``(out, lse)`` with lse fp32 (B,Hq,Nq) =
-    natural-log of the softmax denominator.  ``split_tail`` (opt-in) lets the launcher split the
-    key range of the trailing query rows to fill the last wave of CTAs (non-causal (B,H,N,D) calls
-    only; worth about 3 % at B=2 H=8 N=8192 and a loss for short launches, where the extra launches
-    cost more host time than the idle SMs).
+    natural-log of the softmax denominator.  ``balance`` (default on) launches through
+    ``miniattn_fwd_balanced``: when the work items do not fill a whole number of rounds of one CTA
+    per SM, the key range of some items is cut over several CTAs inside the one launch (scratch for
+    their partial results is cached per device and stream).
     """
-    plan = None
-    if split_tail and layout == "bhnd" and not causal and not return_lse and kernel in ("auto", "ws") \
-            and q.is_cuda and q.dim() == 4 and k.dim() == 4:
-        plan = _tail_plan(q.shape[0], q.shape[1], q.shape[2], k.shape[2], _sm_count(q.device))
-    if plan is not None:
-        return _forward_split_tail(q, k, v, softmax_scale, out, kernel, plan)
     p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0)
     if p is not None:
         with torch.cuda.device(q.device):
             stream = torch.cuda.current_stream(q.device).cuda_stream
-            rc = _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
+            need = _lib.lib.miniattn_fwd_balanced_scratch_bytes(C.byref(p)) if balance else 0
+            if need < 0:
+                _lib.check(int(need), "miniattn_fwd_balanced_scratch_bytes")
+            if need > 0:
+                scratch = _scratch_for(q.device, stream, int(need))
+                rc = _lib.lib.miniattn_fwd_balanced(C.byref(p), C.c_void_p(scratch.data_ptr()),
+                                                    C.c_size_t(scratch.numel()), C.c_void_p(stream))
+            else:
+                rc = _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
         _lib.check(rc, "miniattn_fwd")
     return (out, lse) if return_lse else out
-
-
-# ---- filling the last wave -----------------------------------------------------------------
-# The kernel runs one CTA per pair of 128-row Q tiles, one CTA per SM.  When the number of CTAs is
-# not a multiple of the SM count the last wave leaves SMs idle (512 CTAs on 148 SMs: 3.46 waves of
-# work take 4).  The launcher therefore cuts the query rows in two: the leading rows fill whole
-# waves; the trailing rows run concurrently on a second stream with their key range split into
-# kSplit pieces (small CTAs that pack the idle SMs), followed by a one-pass merge of the partials.
-kSplit = 4
-_sm_counts: dict = {}
-_split_ctx: dict = {}
-
-
-def _sm_count(device: torch.device) -> int:
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _sm_counts:
-        _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    return _sm_counts[idx]
-
-
-def _tail_plan(B: int, Hq: int, Nq: int, Nk: int, sms: int):
-    """Rows [0, split_row) go to the main launch, the rest is split over the keys.  None = do not split."""
-    heads = B * Hq
-    n_pairs = (Nq + 255) // 256
-    items = n_pairs * heads
-    if heads == 0 or items <= sms or items % sms == 0:
-        return None
-    if (items % sms) / sms > 0.85:          # the last wave is nearly full anyway
-        return None
-    main_pairs = (items // sms) * sms // heads
-    if main_pairs <= 0 or main_pairs >= n_pairs:
-        return None
-    kv_tiles = (Nk + 127) // 128
-    if kv_tiles < 8 * kSplit:               # pieces would be too short to amortise a CTA
-        return None
-    piece = ((kv_tiles + kSplit - 1) // kSplit) * 128
-    return main_pairs * 256, piece
-
-
-def _forward_split_tail(q, k, v, softmax_scale, out, kernel, plan):
-    split_row, piece = plan
-    B, Hq, Nq, D = q.shape
-    Nk = k.shape[2]
-    if out is None:
-        out = torch.empty_like(q)
-    dev = q.device
-    rows_tail = Nq - split_row
-    bounds = [(a, min(Nk, a + piece)) for a in range(0, Nk, piece)]
-    key = (dev.index, B, Hq, rows_tail, D, q.dtype, len(bounds))
-    ctx = _split_ctx.get(key)
-    if ctx is None:
-        ctx = _split_ctx[key] = dict(
-            streams=[torch.cuda.Stream(dev) for _ in bounds],
-            part_o=torch.empty((len(bounds), B, Hq, rows_tail, D), dtype=q.dtype, device=dev),
-            part_lse=torch.empty((len(bounds), B, Hq, rows_tail), dtype=torch.float32, device=dev))
-    sides = ctx["streams"]  # one stream per key piece: the piece launches must overlap each other
-    side = sides[0]
-    main = torch.cuda.current_stream(dev)
-    for st in sides:
-        st.wait_stream(main)
-    # main part on the caller's stream
-    p, _, _ = _prepare(q[:, :, :split_row], k, v, False, softmax_scale, "bhnd", False, out[:, :, :split_row],
-                       kernel, 0, 0)
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(main.cuda_stream)), "miniattn_fwd")
-        # tail rows: one launch per key piece on the side stream, then the merge
-        qt = q[:, :, split_row:]
-        for i, (a, b_) in enumerate(bounds):
-            pp, _, _ = _prepare(qt, k[:, :, a:b_], v[:, :, a:b_], False, softmax_scale, "bhnd", False,
-                                ctx["part_o"][i], kernel, 0, 0)
-            pp.lse = ctx["part_lse"][i].data_ptr()
-            _lib.check(_lib.lib.miniattn_fwd(C.byref(pp), C.c_void_p(sides[i].cuda_stream)), "miniattn_fwd")
-        for st in sides[1:]:
-            side.wait_stream(st)
-        m = _lib.MergeSplitParams()
-        m.part_o, m.part_lse = ctx["part_o"].data_ptr(), ctx["part_lse"].data_ptr()
-        ot = out[:, :, split_row:]
-        m.out, m.lse_out = ot.data_ptr(), None
-        m.rows, m.n, m.D, m.dtype = B * Hq * rows_tail, len(bounds), D, _DTYPES[q.dtype]
-        if ot.is_contiguous():
-            m.out_rows_per_slab, m.out_slab_stride = 0, 0
-        else:
-            if not (ot.stride(3) == 1 and ot.stride(2) == D and ot.stride(0) == ot.stride(1) * Hq):
-                raise RuntimeError("out must be a contiguous (B,H,N,D) tensor for the split-tail launch")
-            m.out_rows_per_slab, m.out_slab_stride = rows_tail, ot.stride(1)
-        _lib.check(_lib.lib.miniattn_merge_split(C.byref(m), C.c_void_p(side.cuda_stream)), "miniattn_merge_split")
-    main.wait_stream(side)
-    return out
 
 
 class Int8QK:

@@ -258,19 +258,6 @@ def test_host_buffer_pipeline():
         miniattn.flash_attn_fwd_host(q, kh, vh)
 
 
-def test_split_tail_launcher_matches_single_launch():
-    """Opt-in split of the trailing rows' key range (fills the last wave of CTAs): same result."""
-    q, k, v = make_inputs(2, 8, 8, 4096, 4096, 128, torch.float16, seed=31)
-    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
-    from miniattn.ops import _tail_plan, _sm_count
-    assert _tail_plan(2, 8, 4096, 4096, 148) == (2304, 1024)
-    one = miniattn.flash_attn_fwd(qd, kd, vd)
-    two = miniattn.flash_attn_fwd(qd, kd, vd, split_tail=True)
-    torch.cuda.synchronize()
-    assert maxerr(one, two) <= 1e-3
-    assert miniattn.device_status(DEV) == 0
-
-
 def test_random_shapes_against_oracle():
     """Seeded sweep over shapes, head groupings, offsets and dtypes (both kernels)."""
     g = torch.Generator().manual_seed(2024)
