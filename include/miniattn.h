@@ -211,27 +211,6 @@ typedef struct MiniAttnMergeParams {
 int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream);
 
 /*
- * One-pass merge of n normalised partials of the same query rows (no reference counterpart; same
- * arithmetic as above over n terms).  Used when the key range of some work items is split over
- * several CTAs to fill the last wave of a launch.
- */
-typedef struct MiniAttnMergeSplitParams {
-  const void*  part_o;    /* [n, rows, D] 16-bit normalised partials, contiguous              */
-  const float* part_lse;  /* [n, rows] fp32 log-sum-exp of each partial (-inf = empty)         */
-  void*        out;       /* [rows, D] 16-bit merged result (contiguous, or slabs: see below)  */
-  float*       lse_out;   /* optional [rows] fp32 merged log-sum-exp                           */
-  int64_t rows;
-  int32_t n;              /* number of partials, 1..64                                         */
-  int32_t D;
-  int32_t dtype;          /* MINIATTN_FP16 | MINIATTN_BF16                                     */
-  int32_t reserved;
-  int64_t out_rows_per_slab; /* as in MiniAttnMergeParams                                      */
-  int64_t out_slab_stride;
-} MiniAttnMergeSplitParams;
-
-int miniattn_merge_split(const MiniAttnMergeSplitParams* p, void* stream);
-
-/*
  * Failure-detection self-test (no reference counterpart; the reference never checks
  * its launches, flash_attention.cu:123).  Launches one CTA that waits on a barrier
  * nothing signals.  The wait gives up after `limit_ns` nanoseconds (0 < limit_ns <= 2e9),

@@ -30,9 +30,6 @@ cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs
                             const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk, float q_fold,
                             int8_t* q8, int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
                             cudaStream_t st);
-cudaError_t launch_merge_n(const void* part_o, const float* part_lse, int n, void* out, float* lse_out,
-                           long long rows, int D, bool bf16, long long rows_per_slab,
-                           long long out_slab_stride, int sm_count, cudaStream_t st);
 long long static_colsum_capacity();
 cudaError_t launch_quant_qk_static(int D, bool bf16, const void* q, const long long* qs, const void* k,
                                    const long long* ks, int B, int Hq, int Hkv, int Nq, int Nk,
@@ -516,37 +513,6 @@ int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream) {
                                             p->rows, p->D, p->dtype == MINIATTN_BF16, p->init,
                                             rows_per_slab, slab_stride, sms,
                                             reinterpret_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess)
-    return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
-  return MINIATTN_OK;
-}
-
-int miniattn_merge_split(const MiniAttnMergeSplitParams* p, void* stream) {
-  g_err[0] = 0;
-  if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
-  if (p->rows < 0 || p->n < 1 || p->n > 64) return fail(MINIATTN_EINVAL, "rows must be >= 0 and 1 <= n <= 64");
-  if (p->D != 64 && p->D != 128)
-    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64 or 128)", p->D);
-  if (p->dtype != MINIATTN_FP16 && p->dtype != MINIATTN_BF16)
-    return fail(MINIATTN_EUNSUPPORTED, "dtype must be fp16 (0) or bf16 (1), got %d", p->dtype);
-  if (p->rows == 0) return MINIATTN_OK;
-  if (!p->part_o || !p->part_lse || !p->out) return fail(MINIATTN_EINVAL, "part_o, part_lse and out must not be null");
-  if (reinterpret_cast<uintptr_t>(p->part_o) % 16 || reinterpret_cast<uintptr_t>(p->out) % 16)
-    return fail(MINIATTN_EINVAL, "part_o and out must be 16-byte aligned");
-  long long rows_per_slab = p->rows, slab_stride = p->rows * p->D;
-  if (p->out_rows_per_slab > 0) {
-    if (p->rows % p->out_rows_per_slab != 0)
-      return fail(MINIATTN_EINVAL, "rows must be a multiple of out_rows_per_slab");
-    if (p->out_slab_stride < p->out_rows_per_slab * p->D || p->out_slab_stride % 8 != 0)
-      return fail(MINIATTN_EINVAL, "out_slab_stride must be a multiple of 8 elements and cover a slab");
-    rows_per_slab = p->out_rows_per_slab;
-    slab_stride = p->out_slab_stride;
-  }
-  int sms = 0, rc;
-  if ((rc = check_device(&sms)) != 0) return rc;
-  cudaError_t e = ma::launch_merge_n(p->part_o, p->part_lse, p->n, p->out, p->lse_out, p->rows, p->D,
-                                     p->dtype == MINIATTN_BF16, rows_per_slab, slab_stride, sms,
-                                     reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;

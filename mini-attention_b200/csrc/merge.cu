@@ -106,74 +106,6 @@ merge_partials_kernel(float* __restrict__ acc_o, float* __restrict__ acc_lse,
   }
 }
 
-// One-pass merge of n normalised partials of the same rows (split-KV of the tail work items):
-// part_o [n][rows][D] 16 bit, part_lse [n][rows]; out gets the merged rows (strided slabs as above),
-// lse_out (optional) their log-sum-exp.  Per row D*2*(n+1) bytes of traffic.
-template <int VEC, bool BF16>
-__global__ void __launch_bounds__(256)
-merge_n_kernel(const uint16_t* __restrict__ part_o, const float* __restrict__ part_lse, int n,
-               uint16_t* __restrict__ out, float* __restrict__ lse_out, long long rows,
-               long long rows_per_slab, long long out_slab_stride) {
-  constexpr int D = 32 * VEC;
-  const int lane = threadIdx.x & 31;
-  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < rows;
-       row += warps) {
-    float m = -INFINITY;
-    for (int i = 0; i < n; ++i) m = fmaxf(m, part_lse[i * rows + row]);
-    const float ms = (m == -INFINITY) ? 0.f : m;
-    float acc[VEC];
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
-    float den = 0.f;
-    for (int i = 0; i < n; ++i) {
-      const float w = __expf(part_lse[i * rows + row] - ms);
-      den += w;
-      const uint16_t* src = part_o + (static_cast<long long>(i) * rows + row) * D;
-      if constexpr (VEC == 4) {
-        const uint2 u = *reinterpret_cast<const uint2*>(src + lane * 4);
-        const float2 a = unpack2<BF16>(u.x), b = unpack2<BF16>(u.y);
-        acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
-      } else {
-        const float2 a = unpack2<BF16>(*reinterpret_cast<const uint32_t*>(src + lane * 2));
-        acc[0] += w * a.x; acc[1] += w * a.y;
-      }
-    }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    uint16_t* orow = out + (row / rows_per_slab) * out_slab_stride + (row % rows_per_slab) * D;
-    if constexpr (VEC == 4) {
-      uint2 u;
-      u.x = pack2f<BF16>(acc[0] * inv, acc[1] * inv);
-      u.y = pack2f<BF16>(acc[2] * inv, acc[3] * inv);
-      *reinterpret_cast<uint2*>(orow + lane * 4) = u;
-    } else {
-      *reinterpret_cast<uint32_t*>(orow + lane * 2) = pack2f<BF16>(acc[0] * inv, acc[1] * inv);
-    }
-    if (lse_out != nullptr && lane == 0) lse_out[row] = den > 0.f ? ms + __logf(den) : -INFINITY;
-  }
-}
-
-cudaError_t launch_merge_n(const void* part_o, const float* part_lse, int n, void* out, float* lse_out,
-                           long long rows, int D, bool bf16, long long rows_per_slab,
-                           long long out_slab_stride, int sm_count, cudaStream_t st) {
-  if (rows == 0) return cudaSuccess;
-  const long long blocks_needed = (rows + 7) / 8;
-  const long long cap = static_cast<long long>(sm_count) * 8;
-  const unsigned grid = static_cast<unsigned>(blocks_needed < cap ? blocks_needed : cap);
-  const uint16_t* po = static_cast<const uint16_t*>(part_o);
-  uint16_t* oo = static_cast<uint16_t*>(out);
-  if (D == 128) {
-    if (bf16) merge_n_kernel<4, true><<<grid, 256, 0, st>>>(po, part_lse, n, oo, lse_out, rows, rows_per_slab, out_slab_stride);
-    else merge_n_kernel<4, false><<<grid, 256, 0, st>>>(po, part_lse, n, oo, lse_out, rows, rows_per_slab, out_slab_stride);
-  } else if (D == 64) {
-    if (bf16) merge_n_kernel<2, true><<<grid, 256, 0, st>>>(po, part_lse, n, oo, lse_out, rows, rows_per_slab, out_slab_stride);
-    else merge_n_kernel<2, false><<<grid, 256, 0, st>>>(po, part_lse, n, oo, lse_out, rows, rows_per_slab, out_slab_stride);
-  } else {
-    return cudaErrorInvalidValue;
-  }
-  return cudaGetLastError();
-}
-
 cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part_o,
                                   const float* part_lse, void* out, long long rows, int D, bool bf16,
                                   int init, long long rows_per_slab, long long out_slab_stride,

@@ -77,6 +77,10 @@ float cta_cost(int D) {
   static const float v = env_or("MINIATTN_PLAN_CTA_COST", -1.f);
   return v >= 0.f ? v : (D == 128 ? 2.0f : 3.0f);
 }
+float grade_frac() {  // MINIATTN_PLAN_GRADE: spread of the per-SM targets, as a fraction of T
+  static const float v = env_or("MINIATTN_PLAN_GRADE", 0.015f);
+  return v;
+}
 float piece_cost() {
   static const float v = env_or("MINIATTN_PLAN_PIECE_COST", 1.3f);
   return v;
@@ -106,7 +110,7 @@ bool fill(const std::vector<int>& w, int sms, float T, float h, float fee, std::
     heap.pop();
   }
   std::vector<int> placed(sms, 0);
-  const float grade = 0.015f * T;
+  const float grade = grade_frac() * T;
   int si = 0;
   for (; i < n; ++i) {
     int t0 = 0;

@@ -52,16 +52,6 @@ class MergeParams(C.Structure):
     ]
 
 
-class MergeSplitParams(C.Structure):
-    """Mirror of ``MiniAttnMergeSplitParams``."""
-
-    _fields_ = [
-        ("part_o", C.c_void_p), ("part_lse", C.c_void_p), ("out", C.c_void_p), ("lse_out", C.c_void_p),
-        ("rows", C.c_int64), ("n", C.c_int32), ("D", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32),
-        ("out_rows_per_slab", C.c_int64), ("out_slab_stride", C.c_int64),
-    ]
-
-
 class PlanInfo(C.Structure):
     """Mirror of ``MiniAttnPlanInfo``."""
 
@@ -102,8 +92,6 @@ def _load() -> C.CDLL:
         getattr(lib, name).restype = C.c_int
     lib.miniattn_merge_partials.argtypes = [C.POINTER(MergeParams), C.c_void_p]
     lib.miniattn_merge_partials.restype = C.c_int
-    lib.miniattn_merge_split.argtypes = [C.POINTER(MergeSplitParams), C.c_void_p]
-    lib.miniattn_merge_split.restype = C.c_int
     lib.miniattn_selftest_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     lib.miniattn_selftest_wait.restype = C.c_int
     lib.miniattn_version.restype = C.c_char_p

@@ -75,31 +75,3 @@ def test_shard_mode_rank_by_rank():
         par.sharded_forward(qd, kd, vd, causal=True, rank=r, world=4, out=out)
     ref = attention_reference(q, k, v, causal=True, out_dtype=torch.float32)
     assert (out.float().cpu() - ref).abs().max().item() <= TOL[torch.bfloat16]
-
-
-def test_n_way_split_merge_matches_pairwise_oracle():
-    """miniattn_merge_split (one pass over n partials) against the oracle's pairwise merge."""
-    import ctypes as C
-    from miniattn import _lib
-    g = torch.Generator().manual_seed(3)
-    n, B, H, R, D = 3, 2, 2, 40, 128
-    po = torch.randn(n, B, H, R, D, generator=g).half()
-    pl = torch.randn(n, B, H, R, generator=g) * 3
-    pl[1, 0, 0, :4] = float("-inf")
-    ref_o, ref_l = po[0].float(), pl[0].clone()
-    for i in range(1, n):
-        ref_o, ref_l = merge_partials(ref_o, ref_l, po[i], pl[i])
-    big = torch.zeros(B, H, 100, D, dtype=torch.float16, device=DEV)
-    view = big[:, :, 60:]  # strided output: a token range of a larger tensor
-    lse = torch.empty(B, H, R, dtype=torch.float32, device=DEV)
-    pod, pld = po.to(DEV), pl.to(DEV)
-    m = _lib.MergeSplitParams()
-    m.part_o, m.part_lse, m.out, m.lse_out = pod.data_ptr(), pld.data_ptr(), view.data_ptr(), lse.data_ptr()
-    m.rows, m.n, m.D, m.dtype = B * H * R, n, D, 0
-    m.out_rows_per_slab, m.out_slab_stride = R, view.stride(1)
-    rc = _lib.lib.miniattn_merge_split(C.byref(m), C.c_void_p(torch.cuda.current_stream().cuda_stream))
-    assert rc == 0, _lib.last_error()
-    torch.cuda.synchronize()
-    assert (view.float().cpu() - ref_o).abs().max().item() <= 2e-3
-    assert (lse.cpu() - ref_l).abs().max().item() <= 1e-5
-    assert torch.all(big[:, :, :60] == 0)
