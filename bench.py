@@ -411,7 +411,8 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": scaling,
-            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "vs_baseline": None, "dtype": ("int8 QK^T (s32 acc) + " + w["dtype"] + " PV" if w.get("int8qk") else w["dtype"]),
+            "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu": shard, "seq_len": N, "head_dim": D, "causal": causal,
                        "parallelism": (f"zig-zag ring over {world} GPU(s): NCCL send/recv of K/V pairs + LSE merge" if ring
                                        else f"batch x head shards over {world} GPU(s), no communication"),

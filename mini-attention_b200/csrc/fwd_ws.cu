@@ -282,13 +282,13 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tmem_wait_ld();
           if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 2);
           if constexpr (QK8) {
-            // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding
-            // the bit pattern of 1.5*2^23 and subtracting that value is exact.
+            // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding the
+            // bit pattern of 1.5*2^23 gives the float 12582912 + acc exactly.  The offset stays in:
+            // it is order-preserving for the maximum and folds into the constant of the exp2 FMA.
 #pragma unroll
             for (int q = 0; q < 2; ++q)
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                s[q][i] = __float_as_uint(__uint_as_float(s[q][i] + 0x4B400000u) - 12582912.f);
+              for (int i = 0; i < 32; ++i) s[q][i] += 0x4B400000u;
           }
           const int lim = vis_row - (kv_t0 + j) * kTileN - hb * kHalfN;
           if (lim < kHalfN) {  // diagonal or ragged half: hide the keys this row must not see
@@ -309,7 +309,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             mx4[q] = m;
           }
           // running maximum m_cur is kept in log2 units (raw maximum * cj)
-          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * cj;
+          constexpr float kBias = QK8 ? 12582912.f : 0.f;
+          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          if constexpr (QK8) mx -= kBias;
+          mx *= cj;
           float alpha = 1.f;
           if (j == 0 && hb == 0) {
             m_cur = mx;
@@ -324,7 +327,9 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           warp_arrive(bar(L::kBarAlpha + 2 * t + hb));
           if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 3);
 
-          const float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
+          // exponent of a score x: x*cj - m; for the int8 variant x carries kBias, taken out here
+          float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
+          if constexpr (QK8) mc = fmaf(kBias, cj, mc);
           float psum0 = 0.f, psum1 = 0.f;
           uint32_t pk[32];
 #pragma unroll
