@@ -200,25 +200,58 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     n_tiles = pe_t1 - pe_t0;
   }
 
-  if (warp == 13 && lane == 0) {
-    mbar_init(bar(L::kBarQFull + 0), 1);
-    mbar_init(bar(L::kBarQFull + 1), 1);
-    for (int s = 0; s < L::kStages; ++s) {
-      mbar_init(bar(L::kBarKvFull + s), 1);
-      mbar_init(bar(L::kBarKvEmpty + s), nt);  // one release per issuing thread
+  // TMA loads (issued by lane 0 of warp 13 only): Q tile t; ring fill i = K (even) or V (odd) of
+  // K/V tile kv_t0 + i/2 into slot i % kStages.
+  auto load_q = [&](int t) {
+    if constexpr (QK8) {  // one box of D bytes x 128 rows
+      mbar_expect_tx(bar(L::kBarQFull + t), kTileM * D);
+      tma_load_4d(sQ + t * L::kTileBytes, &tm_q, bar(L::kBarQFull + t), 0, q0 + t * kTileM, h, b);
+    } else {
+      mbar_expect_tx(bar(L::kBarQFull + t), L::kTileBytes);
+#pragma unroll
+      for (int bx = 0; bx < L::kBoxes; ++bx)
+        tma_load_4d(sQ + t * L::kTileBytes + bx * kBoxBytes, &tm_q, bar(L::kBarQFull + t),
+                    bx * kBoxCols, q0 + t * kTileM, h, b);
     }
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(bar(L::kBarSFull + i), 1);
-      mbar_init(bar(L::kBarPReady + i), 4);
-      mbar_init(bar(L::kBarAlpha + i), 4);
-      mbar_init(bar(L::kBarOReady + i), 4);
-      mbar_init(bar(L::kBarODone + i), 1);
+  };
+  auto load_kv = [&](int i) {
+    const int slot = i % L::kStages;
+    const uint32_t fb = bar(L::kBarKvFull + slot);
+    const int j = kv_t0 + (i >> 1);
+    if (QK8 && !(i & 1)) {  // int8 K tile: one box of D bytes x 128 rows
+      mbar_expect_tx(fb, kTileN * D);
+      tma_load_4d(sRing + slot * L::kTileBytes, &tm_k, fb, 0, j * kTileN, hk, b);
+    } else {
+      mbar_expect_tx(fb, L::kTileBytes);
+      const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
+#pragma unroll
+      for (int bx = 0; bx < L::kBoxes; ++bx)
+        tma_load_4d(sRing + slot * L::kTileBytes + bx * kBoxBytes, tm, fb, bx * kBoxCols, j * kTileN, hk, b);
     }
-    *abort_flag = 0;
+  };
+  const int n_fill = 2 * n_tiles;
+  const int n_early = min(n_fill, L::kStages);  // first use of every ring slot: nothing to wait for
+
+  if (warp == 13) {
+    // one barrier per lane: arrival counts by index range
+    for (int i = lane; i < L::kNumBars; i += 32) {
+      uint32_t count = 1;  // Q full, K/V full, S full, O done: one arrival (a TMA or MMA commit)
+      if (i >= L::kBarKvEmpty && i < L::kBarSFull) count = nt;      // one release per issuing thread
+      else if (i >= L::kBarPReady && i < L::kBarODone) count = 4;   // P ready, alpha, O ready: 4 warps
+      mbar_init(bar(i), count);
+    }
+    if (lane == 0) *abort_flag = 0;
     fence_mbar_init();
-    prefetch_tmap(&tm_q);
-    prefetch_tmap(&tm_k);
-    prefetch_tmap(&tm_v);
+    __syncwarp();
+  }
+  if (warp == 13 && lane == 0) {
+    fence_proxy_async_smem();
+    // The first loads start here, before TMEM is allocated and the CTA synchronises: their
+    // latency overlaps the rest of the set-up.
+    if (n_tiles > 0) {
+      for (int t = 0; t < nt; ++t) load_q(t);
+      for (int i = 0; i < n_early; ++i) load_kv(i);
+    }
     prefetch_tmap(&tm_o);
   }
   if (warp == 12) {
@@ -526,7 +559,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           for (int bx = 0; bx < L::kBoxes; ++bx)
             tma_store_4d(&tm_o, stage + bx * kBoxBytes, bx * kBoxCols, q0 + t * kTileM, h, b);
           tma_store_commit();
-          tma_store_wait_all();
+          tma_store_wait_read0();  // the staging buffer must outlive the copy's reads, no more
           MA_STAMP(t, 27);
         }
       }
@@ -664,36 +697,11 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     } else if (warp == 13) {
       // =========================== TMA producer ====================================
       if (lane == 0 && n_tiles > 0) {
-        for (int t = 0; t < nt; ++t) {
-          if constexpr (QK8) {  // one box of D bytes x 128 rows
-            mbar_expect_tx(bar(L::kBarQFull + t), kTileM * D);
-            tma_load_4d(sQ + t * L::kTileBytes, &tm_q, bar(L::kBarQFull + t), 0, q0 + t * kTileM, h, b);
-          } else {
-            mbar_expect_tx(bar(L::kBarQFull + t), L::kTileBytes);
-#pragma unroll
-            for (int bx = 0; bx < L::kBoxes; ++bx)
-              tma_load_4d(sQ + t * L::kTileBytes + bx * kBoxBytes, &tm_q, bar(L::kBarQFull + t),
-                          bx * kBoxCols, q0 + t * kTileM, h, b);
-          }
-        }
-        const int n_fill = 2 * n_tiles;
-        for (int i = 0; i < n_fill; ++i) {
+        for (int i = n_early; i < n_fill; ++i) {
           const int slot = i % L::kStages;
           const int use = i / L::kStages;
-          if (use > 0) mbar_wait(bar(L::kBarKvEmpty + slot), (use - 1) & 1, wc, kErrWaitFree);
-          const uint32_t fb = bar(L::kBarKvFull + slot);
-          const int j = kv_t0 + (i >> 1);
-          if (QK8 && !(i & 1)) {  // int8 K tile: one box of D bytes x 128 rows
-            mbar_expect_tx(fb, kTileN * D);
-            tma_load_4d(sRing + slot * L::kTileBytes, &tm_k, fb, 0, j * kTileN, hk, b);
-          } else {
-            mbar_expect_tx(fb, L::kTileBytes);
-            const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
-#pragma unroll
-            for (int bx = 0; bx < L::kBoxes; ++bx)
-              tma_load_4d(sRing + slot * L::kTileBytes + bx * kBoxBytes, tm, fb, bx * kBoxCols,
-                          j * kTileN, hk, b);
-          }
+          mbar_wait(bar(L::kBarKvEmpty + slot), (use - 1) & 1, wc, kErrWaitFree);
+          load_kv(i);
         }
         // On the give-up path copies may still be in flight: let them land (bounded)
         // before the CTA's shared memory is released.
