@@ -378,6 +378,19 @@ def main():
         pre_bytes = (sHq + 2 * sHkv) * sB * sN * D * 2 + (sHq + sHkv) * sB * sN * D
         extra["attention_only"] = {"ms": ms_a, "tflops": step_flops / ms_a / 1e9}
         extra["prepass_only"] = {"ms": ms_p, "algorithmic_bytes": pre_bytes, "hbm_gbs": pre_bytes / ms_p / 1e6}
+        # Half of the flops (Q K^T) may run at the int8 rate, half (P V) at the 16-bit rate:
+        # t >= F/2/P_int8 + F/2/P_16.  No int8 peak is measured on this pool; twice the measured
+        # 16-bit peak stands in for it (the ratio of the nominal dense figures, 4.5 / 2.25 PFLOP/s).
+        peak16, _ = measured_peak()
+        t_bound_ms = (step_flops / 2 / (2 * peak16 * 1e12) + step_flops / 2 / (peak16 * 1e12)) * 1e3
+        extra["int8_blended_bound"] = {"ms": t_bound_ms, "frac_attention_only": t_bound_ms / ms_a,
+                                       "int8_peak_assumed_tflops": 2 * peak16}
+        # At D = 64 the exponentials bound the kernel before the tensor pipe does: one exp2 per
+        # score, 16 per clock per SM (the special-function unit), at the maximum SM clock.
+        props = torch.cuda.get_device_properties(dev)
+        mhz = (clocks or {}).get("sm_max_mhz") or 1965.0
+        t_exp_ms = (sB * sHq * sN * sN * (0.5 if causal else 1.0)) / (16.0 * props.multi_processor_count * mhz * 1e6) * 1e3
+        extra["exp2_bound"] = {"ms": t_exp_ms, "frac_attention_only": t_exp_ms / ms_a}
     sweep = {}
     if args.workload == "c2" and rank == 0 and not args.no_sweep:
         for n in SWEEP_N:
