@@ -339,6 +339,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    last_median = [0.0]
+
     def timed(fn, steps, warmup):
         for _ in range(warmup):
             flush.zero_()
@@ -351,7 +353,9 @@ def main():
             fn()
             b_.record(stream)
         barrier()
-        ms = sum(a.elapsed_time(b_) for a, b_ in evs)
+        per_step = [a.elapsed_time(b_) for a, b_ in evs]
+        ms = sum(per_step)
+        last_median[0] = statistics.median(per_step)  # this rank's median step, reported beside the mean
         if world > 1:
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -362,6 +366,7 @@ def main():
     if sampler is not None:
         time.sleep(0.6)  # let nvidia-smi start sampling before the timed region
     ms_dev = timed(step_device, args.steps, args.warmup)
+    ms_dev_median = last_median[0]
     clocks = sampler.stop() if sampler else None
     ms_e2e = ms_dev if args.no_e2e else timed(step_e2e, max(3, args.steps // 2), 3)
     status = miniattn.device_status(dev)
@@ -423,7 +428,8 @@ def main():
         achieved = step_flops / ms_dev / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": scaling,
+            "warmup": args.warmup, "ms_per_step": ms_dev, "ms_per_step_median_rank0": ms_dev_median,
+            "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": ("int8 QK^T (s32 acc) + " + w["dtype"] + " PV" if w.get("int8qk") else w["dtype"]),
             "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu": shard, "seq_len": N, "head_dim": D, "causal": causal,
