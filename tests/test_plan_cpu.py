@@ -101,3 +101,51 @@ def test_empty_and_degenerate_shapes():
     assert plan_info(2, 8, 512, 0, sm_count=SMS)[0].split == 0
     info, _ = plan_info(1, 1, 128, 128, sm_count=SMS)      # one item, one K/V tile: nothing to cut
     assert info.split == 0 and info.n_ctas == 1
+
+
+def test_random_shapes_keep_the_invariants():
+    """Seeded sweep over shapes, masks, offsets and SM counts: whatever the planner decides, the
+    pieces it hands out must tile every item exactly once."""
+    import random
+    rng = random.Random(7)
+    n_split = 0
+    for _ in range(120):
+        B, Hq = rng.randint(1, 3), rng.randint(1, 12)
+        Nq, Nk = rng.randint(1, 40) * rng.choice([100, 128, 256]), rng.randint(1, 60) * rng.choice([100, 128])
+        D = rng.choice([64, 128])
+        causal = rng.random() < 0.5
+        qp = rng.choice([0, 0, max(0, Nk - Nq), rng.randint(0, 3000)]) if causal else 0
+        kp = rng.choice([0, 0, rng.randint(0, 500)]) if causal else 0
+        sms = rng.choice([148, 132, 64, 16])
+        info, pieces = plan_info(B, Hq, Nq, Nk, D, causal=causal, q_pos0=qp, k_pos0=kp, sm_count=sms)
+        n_items = (((Nq + 127) // 128 + 1) // 2) * B * Hq
+        if not info.split:
+            assert info.n_ctas == n_items
+            continue
+        n_split += 1
+        cover = collections.defaultdict(list)
+        for item, t0, t1, part, nparts, slot in pieces:
+            assert info.n_whole <= item < n_items and 0 <= t0 <= t1
+            cover[item].append((t0, t1, nparts, slot))
+        assert len(cover) == n_items - info.n_whole
+        for item, lst in cover.items():
+            lst.sort()
+            w = item_tiles(item, B, Hq, Nq, Nk, causal, qp, kp)
+            assert lst[0][0] == 0 and lst[-1][1] == w and all(a[1] == b_[0] for a, b_ in zip(lst, lst[1:]))
+            assert all(x[2] == len(lst) for x in lst)
+            assert all((x[3] >= 0) == (len(lst) > 1) for x in lst)
+        assert info.est_balanced <= 0.97 * info.est_plain
+    assert n_split >= 20, "the sweep must exercise the cutting path"
+
+
+def test_plan_entry_rejects_bad_arguments():
+    import ctypes as C
+    from miniattn import _lib
+    p = _lib.FwdParams()
+    p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D = 1, 1, 1, 128, 128, 96
+    info = _lib.PlanInfo()
+    assert _lib.lib.miniattn_plan_fwd(C.byref(p), 148, C.byref(info), None, 0) == _lib.EUNSUPPORTED
+    p.D = 128
+    assert _lib.lib.miniattn_plan_fwd(C.byref(p), 148, None, None, 0) == _lib.EINVAL
+    p.Nq = -1
+    assert _lib.lib.miniattn_plan_fwd(C.byref(p), 148, C.byref(info), None, 0) == _lib.EINVAL
