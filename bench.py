@@ -309,7 +309,7 @@ def main():
         hk.copy_((hk.float() + 2.0 * torch.randn(1, 1, 1, D, generator=g)).to(dt))  # per-channel K offset
         k.copy_(hk)
         bufs = miniattn.Int8QK(sB, sHq, sHkv, sN, sN, D, dev)
-        launches_per_step = 4  # column sums, K quantiser, Q quantiser, attention
+        launches_per_step = 3  # Q quantiser + K column sums, K quantiser, attention
 
         def attend():
             miniattn.flash_attn_fwd_int8qk(q, k, v, causal=causal, out=o, buffers=bufs)

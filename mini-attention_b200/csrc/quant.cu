@@ -5,8 +5,9 @@
 //   2. Q and the smoothed K are quantised to int8 with one symmetric fp32 scale per block of 128
 //      tokens: scale = max|x| / 127 over the 128 x D slab (1 for an all-zero slab),
 //      x8 = round-half-even(x / scale), clamped to [-127, 127].
-// Both kernels are HBM-bound byte movers: 16-byte loads, 8-byte int8 stores, grid = one CTA per
-// (128-token block, head, batch).  Algorithmic traffic per element: K 2 B (mean pass) + 2 B + 1 B,
+// Two launches: stage 1 quantises Q and sums the columns of K (independent work, one grid), stage 2
+// smooths and quantises K.  HBM-bound byte movers: 16-byte loads, 8-byte int8 stores, one CTA per
+// (128-token block, head, batch) or per 1024-token column-sum chunk.  Algorithmic traffic per element: K 2 B (mean pass) + 2 B + 1 B,
 // Q 2 B + 1 B, plus 4 B per 128 x D slab for the scale.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -48,12 +49,11 @@ constexpr int kSumRows = 1024;  // tokens per partial column sum
 
 // partial[b, h, chunk, d] = sum over the chunk's tokens of k[b, h, token, d]
 template <int D, bool BF16>
-__global__ void __launch_bounds__(256)
-k_colsum_kernel(const uint16_t* __restrict__ k, long long sb, long long sh, long long sn, int N,
-                float* __restrict__ partial, int n_chunks) {
+__device__ __forceinline__ void colsum_body(const uint16_t* __restrict__ k, long long sb, long long sh,
+                                            long long sn, int N, float* __restrict__ partial,
+                                            int n_chunks, int chunk, int h, int b, int H) {
   constexpr int CPR = D / 8;          // 16-byte chunks per row
   constexpr int RPP = 256 / CPR;      // rows per pass
-  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int col8 = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
   const uint16_t* base = k + b * sb + h * sh;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -73,20 +73,20 @@ k_colsum_kernel(const uint16_t* __restrict__ k, long long sb, long long sh, long
     float s = 0.f;
 #pragma unroll 4
     for (int r = 0; r < RPP; ++r) s += red[r][threadIdx.x];
-    partial[((static_cast<long long>(b) * gridDim.y + h) * n_chunks + chunk) * D + threadIdx.x] = s;
+    partial[((static_cast<long long>(b) * H + h) * n_chunks + chunk) * D + threadIdx.x] = s;
   }
 }
 
 // One CTA per (128-token block, head, batch): x8 = round(x' / scale), x' = x - mean (K) or x (Q).
 template <int D, bool BF16, bool SMOOTH>
-__global__ void __launch_bounds__(256)
-quant_block_kernel(const uint16_t* __restrict__ x, long long sb, long long sh, long long sn, int N,
-                   const float* __restrict__ partial, int n_chunks, int8_t* __restrict__ x8,
-                   float* __restrict__ scale_out, float fold, float* __restrict__ mean_out) {
+__device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long long sb, long long sh,
+                                           long long sn, int N, const float* __restrict__ partial,
+                                           int n_chunks, int8_t* __restrict__ x8,
+                                           float* __restrict__ scale_out, float fold,
+                                           float* __restrict__ mean_out, int blk, int h, int b, int H,
+                                           int n_blocks) {
   constexpr int CPR = D / 8;
   constexpr int PER = 16 * D / 256;  // chunks per thread (128 rows * D/8 chunks / 256 threads)
-  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int H = gridDim.y, n_blocks = gridDim.x;
   __shared__ float mean[D];
   __shared__ float wmax[8];
   if (SMOOTH) {
@@ -149,6 +149,35 @@ quant_block_kernel(const uint16_t* __restrict__ x, long long sb, long long sh, l
   }
 }
 
+// Stage 1, one launch: the Q quantiser (nothing depends on it but the attention kernel) and the
+// partial column sums of K.  Blocks [0, q_blocks) quantise Q, the rest sum K.
+template <int D, bool BF16>
+__global__ void __launch_bounds__(256)
+prepass_stage1_kernel(const uint16_t* __restrict__ q, long long qsb, long long qsh, long long qsn, int Nq,
+                      int Hq, int nqb, int8_t* __restrict__ q8, float* __restrict__ sq, float fold,
+                      const uint16_t* __restrict__ k, long long ksb, long long ksh, long long ksn, int Nk,
+                      int Hkv, int nch, float* __restrict__ partial, int q_blocks) {
+  const int id = blockIdx.x;
+  if (id < q_blocks) {
+    const int blk = id % nqb, h = (id / nqb) % Hq, b = id / (nqb * Hq);
+    quant_body<D, BF16, false>(q, qsb, qsh, qsn, Nq, nullptr, 0, q8, sq, fold, nullptr, blk, h, b, Hq, nqb);
+  } else {
+    const int c = id - q_blocks;
+    const int chunk = c % nch, h = (c / nch) % Hkv, b = c / (nch * Hkv);
+    colsum_body<D, BF16>(k, ksb, ksh, ksn, Nk, partial, nch, chunk, h, b, Hkv);
+  }
+}
+
+// Stage 2: smooth and quantise K (needs every column sum of stage 1).
+template <int D, bool BF16>
+__global__ void __launch_bounds__(256)
+quant_k_kernel(const uint16_t* __restrict__ k, long long sb, long long sh, long long sn, int N,
+               const float* __restrict__ partial, int n_chunks, int8_t* __restrict__ k8,
+               float* __restrict__ scale_out, float* __restrict__ mean_out) {
+  quant_body<D, BF16, true>(k, sb, sh, sn, N, partial, n_chunks, k8, scale_out, 1.0f, mean_out,
+                            blockIdx.x, blockIdx.y, blockIdx.z, gridDim.y, gridDim.x);
+}
+
 // q8/k8: contiguous [B, H, N, D] int8; scales: [B, H, ceil(N/128)] fp32; partial: scratch of
 // B * Hkv * ceil(N/1024) * D floats; k_mean (optional): [B, Hkv, D].
 template <int D, bool BF16>
@@ -157,15 +186,16 @@ static cudaError_t launch_quant_t(const void* q, const long long* qs, const void
                                   int8_t* k8, float* sq, float* sk, float* partial, float* k_mean,
                                   cudaStream_t st) {
   const int nqb = (Nq + 127) / 128, nkb = (Nk + 127) / 128, nch = (Nk + kSumRows - 1) / kSumRows;
-  if (Nk > 0) {
-    k_colsum_kernel<D, BF16><<<dim3(nch, Hkv, B), 256, 0, st>>>(static_cast<const uint16_t*>(k), ks[0], ks[1],
-                                                               ks[2], Nk, partial, nch);
-    quant_block_kernel<D, BF16, true><<<dim3(nkb, Hkv, B), 256, 0, st>>>(
-        static_cast<const uint16_t*>(k), ks[0], ks[1], ks[2], Nk, partial, nch, k8, sk, 1.0f, k_mean);
-  }
-  if (Nq > 0)
-    quant_block_kernel<D, BF16, false><<<dim3(nqb, Hq, B), 256, 0, st>>>(
-        static_cast<const uint16_t*>(q), qs[0], qs[1], qs[2], Nq, nullptr, 0, q8, sq, q_fold, nullptr);
+  const long long q_blocks = static_cast<long long>(nqb) * Hq * B;
+  const long long s_blocks = static_cast<long long>(nch) * Hkv * B;
+  if (q_blocks + s_blocks > 0x7fffffffll) return cudaErrorInvalidValue;
+  if (q_blocks + s_blocks > 0)
+    prepass_stage1_kernel<D, BF16><<<static_cast<unsigned>(q_blocks + s_blocks), 256, 0, st>>>(
+        static_cast<const uint16_t*>(q), qs[0], qs[1], qs[2], Nq, Hq, nqb, q8, sq, q_fold,
+        static_cast<const uint16_t*>(k), ks[0], ks[1], ks[2], Nk, Hkv, nch, partial, static_cast<int>(q_blocks));
+  if (Nk > 0)
+    quant_k_kernel<D, BF16><<<dim3(nkb, Hkv, B), 256, 0, st>>>(static_cast<const uint16_t*>(k), ks[0], ks[1], ks[2],
+                                                             Nk, partial, nch, k8, sk, k_mean);
   return cudaGetLastError();
 }
 
