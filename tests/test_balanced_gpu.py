@@ -87,3 +87,24 @@ def test_c_abi_scratch_contract():
     torch.cuda.synchronize()
     assert (out.float().cpu() - ref).abs().max().item() <= TOL[torch.float16]
     assert miniattn.device_status(DEV) == 0
+
+
+def test_repeated_balanced_launches_stay_one_rounding_from_the_plain_launch():
+    """Which piece of a cut item arrives last varies from launch to launch (other work on the GPU,
+    clocks), so the fp32 merge order does too; a missing fence or a stale counter would show up as
+    an occasional large error.  200 launches with a second stream busy beside them."""
+    q, k, v = make_inputs(2, 8, 8, 1024, 1024, 128, torch.float16, seed=9)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    plain, lse_p = miniattn.flash_attn_fwd(qd, kd, vd, return_lse=True, balance=False)
+    side = torch.cuda.Stream()
+    worst = worst_lse = 0.0
+    for i in range(200):
+        if i % 3 == 2:
+            with torch.cuda.stream(side):
+                miniattn.flash_attn_fwd(qd[:, :1, :512], kd[:, :1, :512], vd[:, :1, :512], balance=False)
+        o, lse = miniattn.flash_attn_fwd(qd, kd, vd, return_lse=True, balance=True)
+        worst = max(worst, (o.float() - plain.float()).abs().max().item())
+        worst_lse = max(worst_lse, (lse - lse_p).abs().max().item())
+    torch.cuda.synchronize()
+    assert miniattn.device_status(DEV) == 0
+    assert worst <= 5e-4 and worst_lse <= 1e-5
