@@ -86,14 +86,16 @@ int miniattn_fwd(const MiniAttnFwdParams* p, void* stream);
  * The kernel runs one CTA per SM, so a launch whose work items do not fill a whole number of
  * rounds leaves SMs idle in the last one (256 items on 148 SMs: 2 rounds for 1.73 rounds of
  * work).  This entry point plans the launch on the host: the key range of some items is cut into
- * pieces that separate CTAs work on; the CTAs of a cut item leave un-normalised partial results
- * in `scratch`, count themselves in on an arrival counter, and the last one to arrive folds the
- * partials together and writes the output.  No CTA waits for another.  When the plan predicts no
+ * pieces that separate CTAs work on; the CTAs of a cut item count themselves in on an arrival
+ * counter, all but the last to arrive leave un-normalised partial results in `scratch`, and the
+ * last one folds them into its own and writes the output.  The only wait between CTAs is the last
+ * arriver's for partials that CTAs already running are in the middle of writing (bounded like
+ * every device wait; bit 6 of the status word if it ever runs out).  When the plan predicts no
  * gain (many rounds, or too little work per item) the launch is the plain one and scratch is not
  * touched.  Results equal miniattn_fwd's up to fp32 summation order.
  *
  * scratch: device memory, 256-byte aligned, at least miniattn_fwd_balanced_scratch_bytes(p)
- * bytes.  Its first 8192 bytes (the arrival counters) must be zero before the first launch that
+ * bytes.  Its first 16384 bytes (the arrival counters) must be zero before the first launch that
  * uses it; every launch leaves them zero again, unless a bounded device wait ran out (status
  * word != 0) — clear them before the next launch in that case.  Launches that may overlap on
  * the GPU need separate scratch buffers.  scratch == NULL selects the plain launch.

@@ -241,8 +241,8 @@ std::shared_ptr<const ma::FwdPlan> cached_plan(const ma::FwdArgs& a, int D, int 
   return plan;
 }
 
-constexpr size_t kCounterBytes = 8192;  // 2 * kPlanCap arrival counters, rounded up
-static_assert(2 * ma::kPlanCap * sizeof(int) <= kCounterBytes, "counter region too small");
+constexpr size_t kCounterBytes = 16384;  // (arrived, published) x 2 Q tiles x kPlanCap cut items, rounded up
+static_assert(4 * ma::kPlanCap * sizeof(int) <= kCounterBytes, "counter region too small");
 size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 size_t scratch_bytes_of(const ma::FwdPlan& plan, int D) {
   if (!plan.split) return 0;

@@ -25,7 +25,7 @@ struct FwdArgs {
   // leave their partial result, and the per-item arrival counters (zero between launches).
   float*  part_o;      // [slot][2 tiles][D/4][128 rows][4] fp32, un-normalised O of a piece
   float2* part_ml;     // [slot][2 tiles][128 rows]: (row maximum in log2 units, row sum)
-  int*    counters;    // [cut item][2 tiles]
+  int*    counters;    // [cut item][2 tiles][arrived, published]
 };
 
 // One CTA of a balanced launch, read from the launch's table (kernel parameter space).

@@ -402,32 +402,43 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       bool write_out = true;
       if constexpr (PLAN) {
         if (pe_nparts > 1) {
-          // un-normalised O as [D/4][128 rows][4] fp32 (a warp writes 512 contiguous bytes per
-          // store), and (m, l) of every row
-          const long long my = (static_cast<long long>(pe_slot0 + pe_part) * 2 + t) * kTileM;
-          float4* po = reinterpret_cast<float4*>(a.part_o + my * D) + r;
-#pragma unroll
-          for (int q = 0; q < D / 32; ++q) {
-            uint32_t o[32];
-            tmem_ld32(tO + q * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-              po[(q * 8 + g) * kTileM] =
-                  make_float4(__uint_as_float(o[4 * g]), __uint_as_float(o[4 * g + 1]),
-                              __uint_as_float(o[4 * g + 2]), __uint_as_float(o[4 * g + 3]));
-          }
-          a.part_ml[my + r] = make_float2(m_cur, l_run);
+          // Count in first.  The piece that arrives last keeps its result in TMEM and merges; the
+          // others publish theirs: un-normalised O as [D/4][128 rows][4] fp32 (a warp writes 512
+          // contiguous bytes per store) and (m, l) of every row, then count themselves published.
+          int* cnt = a.counters + 4 * pe_counter + 2 * t;  // [0] arrived, [1] published
+          if (r == 0) arrival[t] = atomicAdd(cnt, 1);
+          named_bar_sync(kBarEpilogue + t, 128);
           if (r == 0) MA_STAMP(t, 21);
-          __threadfence();
-          named_bar_sync(kBarEpilogue + t, 128);
-          if (r == 0) MA_STAMP(t, 22);
-          if (r == 0) arrival[t] = atomicAdd(a.counters + 2 * pe_counter + t, 1);
-          named_bar_sync(kBarEpilogue + t, 128);
-          if (r == 0) MA_STAMP(t, 23);
           write_out = (arrival[t] == pe_nparts - 1);
-          if (write_out) {
-            if (r == 0) a.counters[2 * pe_counter + t] = 0;  // leave the counter as it was found
+          if (!write_out) {
+            const long long my = (static_cast<long long>(pe_slot0 + pe_part) * 2 + t) * kTileM;
+            float4* po = reinterpret_cast<float4*>(a.part_o + my * D) + r;
+#pragma unroll
+            for (int q = 0; q < D / 32; ++q) {
+              uint32_t o[32];
+              tmem_ld32(tO + q * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                po[(q * 8 + g) * kTileM] =
+                    make_float4(__uint_as_float(o[4 * g]), __uint_as_float(o[4 * g + 1]),
+                                __uint_as_float(o[4 * g + 2]), __uint_as_float(o[4 * g + 3]));
+            }
+            a.part_ml[my + r] = make_float2(m_cur, l_run);
+            __threadfence();
+            named_bar_sync(kBarEpilogue + t, 128);
+            if (r == 0) atomicAdd(cnt + 1, 1);
+            if (r == 0) MA_STAMP(t, 22);
+          } else {
+            // Every other piece has counted in, so it is publishing right now or has finished:
+            // a short, bounded wait for the last of them, then the counters go back to zero.
+            if (r == 0) {
+              count_wait(cnt + 1, pe_nparts - 1, wc, kErrWaitPeer);
+              cnt[0] = 0;
+              cnt[1] = 0;
+            }
+            named_bar_sync(kBarEpilogue + t, 128);
+            if (r == 0) MA_STAMP(t, 23);
             __threadfence();
             // The other pieces' partials come in through the K/V ring (this tile's half of it),
             // one bulk copy each; the ring is free once the other Q tile's MMAs are done too.

@@ -63,7 +63,7 @@ float list_schedule(const std::vector<float>& cost, int sms, std::vector<float>*
   return end;
 }
 
-constexpr int kMinPiece = 2;       // K/V tiles; shorter pieces cost more than they balance
+constexpr int kMinPiece = 6;       // K/V tiles; shorter pieces cost more than they balance (measured: a 4-tile piece loses)
 constexpr int kMaxParts = 64;      // pieces per item
 
 // Cost model, in steps (one K/V tile of a two-Q-tile CTA, about 2 us at D = 128): fixed cost of
@@ -134,11 +134,13 @@ bool fill(const std::vector<int>& w, int sms, float T, float h, float fee, std::
         if (!whole_fits) {  // a piece of a cut item: it also pays the fee
           const int room = static_cast<int>(std::floor(Ts - load[si] - h - fee));
           if (room < rem) {
-            take = std::min(room, rem - kMinPiece);  // both sides of a cut at least kMinPiece long
-            if (take < kMinPiece) {
+            if (room < kMinPiece) {
               ++si;  // nothing useful fits here any more
               continue;
             }
+            // both sides of a cut at least kMinPiece long; a rest too short to cut stays whole
+            // (and overruns this SM's target by less than kMinPiece)
+            if (rem >= 2 * kMinPiece) take = std::min(room, rem - kMinPiece);
           }
         }
         load[si] += take + h + (whole_fits ? 0.f : fee);
@@ -194,9 +196,13 @@ void plan_fwd(const FwdArgs& a, int D, int sms, FwdPlan* plan) {
   std::vector<Piece> best, cur;
   float best_t = plain;
   int best_whole = 0;
-  const float step = std::max(0.5f, 0.004f * bound);
-  for (int attempt = 0; attempt < 10; ++attempt) {
-    const float T = std::max(bound + 0.75f * (h + fee) + step * attempt, kMinPiece + h + fee);
+  // Targets tried: ten fine steps above the bound (several rounds of items: the answer is close
+  // to it), then eight coarse ones up to about half the heaviest item (few, long items).
+  const int w_max = *std::max_element(w.begin(), w.end());
+  const float fine = std::max(0.5f, 0.004f * bound), coarse = std::max(fine, w_max / 16.f);
+  for (int attempt = 0; attempt < 18; ++attempt) {
+    const float up = attempt < 10 ? fine * attempt : fine * 9 + coarse * (attempt - 9);
+    const float T = std::max(bound + 0.75f * (h + fee) + up, kMinPiece + h + fee);
     if (!fill(w, sms, T, h, fee, &cur)) continue;
     int first_cut = n;
     for (const Piece& p : cur)

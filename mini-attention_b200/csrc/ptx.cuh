@@ -19,6 +19,7 @@ constexpr int kErrWaitO    = 1 << 2;   // O += PV MMA never completed
 constexpr int kErrWaitP    = 1 << 3;   // P tile never published by the softmax role
 constexpr int kErrWaitFree = 1 << 4;   // a ring slot was never released
 constexpr int kErrWaitCorr = 1 << 5;   // correction / epilogue hand-off never happened
+constexpr int kErrWaitPeer = 1 << 6;   // another CTA of a cut work item never published its partial
 constexpr int kErrTest     = 1 << 30;  // raised only by the wait self-test kernel
 
 #ifndef MINIATTN_WAIT_LIMIT_NS
@@ -88,6 +89,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins++ & 0x3F) == 0) {
+      if (*w.abort_flag) return false;
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > w.limit_ns) {
+        *w.abort_flag = 1;
+        if (w.status) atomicOr(w.status, err_bit);
+        return false;
+      }
+    }
+  }
+}
+
+// Bounded wait for a counter in global memory to reach `target` (written by other CTAs that are
+// already running).  Same give-up rule as mbar_wait.
+__device__ __forceinline__ bool count_wait(const int* counter, int target, const WaitCtx& w, int err_bit) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (v >= target) return true;
+    if ((spins++ & 0xF) == 0) {
       if (*w.abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;

@@ -73,7 +73,7 @@ def test_pieces_tile_every_item_once(case):
             assert lst[0][4] == -1
     assert cut == info.n_cut_items and sorted(slots) == list(range(info.n_slots))
     rows = info.n_slots * 2 * 128
-    assert info.scratch_bytes == 8192 + ((rows * 8 + 255) // 256) * 256 + rows * D * 4
+    assert info.scratch_bytes == 16384 + ((rows * 8 + 255) // 256) * 256 + rows * D * 4
     assert info.est_balanced <= 0.97 * info.est_plain
     assert info.n_pieces <= 768
 
