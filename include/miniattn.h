@@ -162,6 +162,10 @@ typedef struct MiniAttnInt8Params {
 int miniattn_quant_qk_int8(const MiniAttnInt8Params* p, void* stream);
 int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream);
 
+/* The INT8-QK attention kernel through the balanced launch: same scratch contract and the same
+ * plan as miniattn_fwd_balanced (size it with miniattn_fwd_balanced_scratch_bytes(&p->fwd)). */
+int miniattn_fwd_int8qk_balanced(const MiniAttnInt8Params* p, void* scratch, size_t scratch_bytes, void* stream);
+
 /*
  * Allocation-free form of the INT8 pre-pass.  It has no counterpart in the reference.
  *

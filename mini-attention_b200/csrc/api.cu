@@ -23,7 +23,7 @@ cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs
                           cudaStream_t st);
 cudaError_t launch_fwd_ws_int8qk(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
                                  int sm_count, cudaStream_t st);
-cudaError_t launch_fwd_ws_plan(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
+cudaError_t launch_fwd_ws_plan(int D, bool bf16, bool qk8, const CUtensorMap* tm, const FwdArgs& a,
                                const FwdPlan& plan, cudaStream_t st);
 void plan_fwd(const FwdArgs& a, int D, int sms, FwdPlan* plan);
 cudaError_t launch_quant_qk(int D, bool bf16, const void* q, const long long* qs, const void* k,
@@ -251,6 +251,22 @@ size_t scratch_bytes_of(const ma::FwdPlan& plan, int D) {
 }
 }  // namespace
 
+// Points the kernel arguments at the three regions of a balanced launch's scratch.
+static int bind_scratch(const ma::FwdPlan& plan, int D, void* scratch, size_t scratch_bytes, ma::FwdArgs* a) {
+  const size_t need = scratch_bytes_of(plan, D);
+  if (scratch_bytes < need)
+    return fail(MINIATTN_EINVAL, "scratch holds %zu bytes, this launch needs %zu "
+                "(miniattn_fwd_balanced_scratch_bytes)", scratch_bytes, need);
+  if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0)
+    return fail(MINIATTN_EINVAL, "scratch must be 256-byte aligned");
+  uint8_t* base = static_cast<uint8_t*>(scratch);
+  const size_t rows = static_cast<size_t>(plan.n_slots) * 2 * ma::kTileM;
+  a->counters = reinterpret_cast<int*>(base);
+  a->part_ml = reinterpret_cast<float2*>(base + kCounterBytes);
+  a->part_o = reinterpret_cast<float*>(base + kCounterBytes + align256(rows * sizeof(float2)));
+  return MINIATTN_OK;
+}
+
 // Forward launch shared by miniattn_fwd and miniattn_fwd_balanced (scratch == nullptr: plain).
 static int fwd_common(const MiniAttnFwdParams* p, void* scratch, size_t scratch_bytes, void* stream) {
   g_err[0] = 0;
@@ -294,18 +310,8 @@ static int fwd_common(const MiniAttnFwdParams* p, void* scratch, size_t scratch_
     std::shared_ptr<const ma::FwdPlan> plan;
     if (scratch != nullptr && has_keys) plan = cached_plan(a, p->D, sms);
     if (plan && plan->split) {
-      const size_t need = scratch_bytes_of(*plan, p->D);
-      if (scratch_bytes < need)
-        return fail(MINIATTN_EINVAL, "scratch holds %zu bytes, this launch needs %zu "
-                    "(miniattn_fwd_balanced_scratch_bytes)", scratch_bytes, need);
-      if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0)
-        return fail(MINIATTN_EINVAL, "scratch must be 256-byte aligned");
-      uint8_t* base = static_cast<uint8_t*>(scratch);
-      const size_t rows = static_cast<size_t>(plan->n_slots) * 2 * ma::kTileM;
-      a.counters = reinterpret_cast<int*>(base);
-      a.part_ml = reinterpret_cast<float2*>(base + kCounterBytes);
-      a.part_o = reinterpret_cast<float*>(base + kCounterBytes + align256(rows * sizeof(float2)));
-      e = ma::launch_fwd_ws_plan(p->D, p->dtype == MINIATTN_BF16, tm, a, *plan, st);
+      if ((rc = bind_scratch(*plan, p->D, scratch, scratch_bytes, &a)) != 0) return rc;
+      e = ma::launch_fwd_ws_plan(p->D, p->dtype == MINIATTN_BF16, false, tm, a, *plan, st);
     } else {
       e = ma::launch_fwd_ws(p->D, p->dtype == MINIATTN_BF16, tm, a, sms, st);
     }
@@ -446,7 +452,7 @@ int miniattn_quant_qk_int8_static(const MiniAttnInt8Params* p, void* stream) {
   return MINIATTN_OK;
 }
 
-int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream) {
+static int int8_common(const MiniAttnInt8Params* p, void* scratch, size_t scratch_bytes, void* stream) {
   g_err[0] = 0;
   int rc = check_int8_params(p, true);
   if (rc != 0) return rc > 0 ? MINIATTN_OK : rc;
@@ -476,11 +482,29 @@ int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream) {
   fill_args(&f, &a);
   a.sq = p->q_scale;
   a.sk = p->k_scale;
-  cudaError_t e = ma::launch_fwd_ws_int8qk(f.D, f.dtype == MINIATTN_BF16, tm, a, sms,
-                                           reinterpret_cast<cudaStream_t>(stream));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  std::shared_ptr<const ma::FwdPlan> plan;
+  if (scratch != nullptr) plan = cached_plan(a, f.D, sms);
+  if (plan && plan->split) {
+    if ((rc = bind_scratch(*plan, f.D, scratch, scratch_bytes, &a)) != 0) return rc;
+    e = ma::launch_fwd_ws_plan(f.D, f.dtype == MINIATTN_BF16, true, tm, a, *plan, st);
+  } else {
+    e = ma::launch_fwd_ws_int8qk(f.D, f.dtype == MINIATTN_BF16, tm, a, sms, st);
+  }
   if (e != cudaSuccess)
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;
+}
+
+int miniattn_fwd_int8qk(const MiniAttnInt8Params* p, void* stream) { return int8_common(p, nullptr, 0, stream); }
+
+int miniattn_fwd_int8qk_balanced(const MiniAttnInt8Params* p, void* scratch, size_t scratch_bytes, void* stream) {
+  if (scratch == nullptr && scratch_bytes != 0) {
+    g_err[0] = 0;
+    return fail(MINIATTN_EINVAL, "scratch is null but scratch_bytes is %zu", scratch_bytes);
+  }
+  return int8_common(p, scratch, scratch_bytes, stream);
 }
 
 int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream) {

@@ -777,11 +777,11 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_c
   return cudaGetLastError();
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool QK8>
 static cudaError_t launch_plan_t(const CUtensorMap* tm, const FwdArgs& a, const FwdPlan& plan,
                                  cudaStream_t st) {
   using L = WsLayout<D>;
-  auto kern = fwd_ws_kernel<D, BF16, false, true>;
+  auto kern = fwd_ws_kernel<D, BF16, QK8, true>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
   if (e != cudaSuccess) return e;
@@ -792,11 +792,18 @@ static cudaError_t launch_plan_t(const CUtensorMap* tm, const FwdArgs& a, const 
   return cudaGetLastError();
 }
 
-// Balanced launch: a.part_o / a.part_ml / a.counters point into the caller's scratch.
-cudaError_t launch_fwd_ws_plan(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a,
+// Balanced launch: a.part_o / a.part_ml / a.counters point into the caller's scratch.  qk8: the
+// INT8-QK variant (tm[0], tm[1] are the int8 Q / K maps).
+cudaError_t launch_fwd_ws_plan(int D, bool bf16, bool qk8, const CUtensorMap* tm, const FwdArgs& a,
                                const FwdPlan& plan, cudaStream_t st) {
-  if (D == 128) return bf16 ? launch_plan_t<128, true>(tm, a, plan, st) : launch_plan_t<128, false>(tm, a, plan, st);
-  if (D == 64) return bf16 ? launch_plan_t<64, true>(tm, a, plan, st) : launch_plan_t<64, false>(tm, a, plan, st);
+  if (D == 128) {
+    if (qk8) return bf16 ? launch_plan_t<128, true, true>(tm, a, plan, st) : launch_plan_t<128, false, true>(tm, a, plan, st);
+    return bf16 ? launch_plan_t<128, true, false>(tm, a, plan, st) : launch_plan_t<128, false, false>(tm, a, plan, st);
+  }
+  if (D == 64) {
+    if (qk8) return bf16 ? launch_plan_t<64, true, true>(tm, a, plan, st) : launch_plan_t<64, false, true>(tm, a, plan, st);
+    return bf16 ? launch_plan_t<64, true, false>(tm, a, plan, st) : launch_plan_t<64, false, false>(tm, a, plan, st);
+  }
   return cudaErrorInvalidValue;
 }
 

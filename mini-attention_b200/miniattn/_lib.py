@@ -87,6 +87,8 @@ def _load() -> C.CDLL:
     lib.miniattn_plan_fwd.argtypes = [C.POINTER(FwdParams), C.c_int, C.POINTER(PlanInfo),
                                       C.POINTER(PlanPiece), C.c_int32]
     lib.miniattn_plan_fwd.restype = C.c_int
+    lib.miniattn_fwd_int8qk_balanced.argtypes = [C.POINTER(Int8Params), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.miniattn_fwd_int8qk_balanced.restype = C.c_int
     for name in ("miniattn_quant_qk_int8", "miniattn_quant_qk_int8_static", "miniattn_fwd_int8qk"):
         getattr(lib, name).argtypes = [C.POINTER(Int8Params), C.c_void_p]
         getattr(lib, name).restype = C.c_int

@@ -219,12 +219,13 @@ def flash_attn_fwd_int8qk(
     buffers: Optional[Int8QK] = None,
     quantize: bool = True,
     attend: bool = True,
+    balance: bool = True,
 ):
     """INT8-QK attention: K is mean-smoothed, Q and K are quantised to int8 per block of 128
     tokens (pre-pass), Q8 K8^T runs on the int8 tensor cores, P V stays 16 bit.  `buffers` lets a
     caller reuse the pre-pass buffers across calls of the same shape (and inspect them);
     ``quantize=False`` skips the pre-pass (buffers already filled), ``attend=False`` runs the
-    pre-pass only."""
+    pre-pass only; ``balance`` as for :func:`flash_attn_fwd`."""
     p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, "auto", 0, 0)
     if p is None:
         return (out, lse) if return_lse else out
@@ -241,7 +242,16 @@ def flash_attn_fwd_int8qk(
         if quantize:
             _lib.check(_lib.lib.miniattn_quant_qk_int8(C.byref(p8), C.c_void_p(stream)), "miniattn_quant_qk_int8")
         if attend:
-            _lib.check(_lib.lib.miniattn_fwd_int8qk(C.byref(p8), C.c_void_p(stream)), "miniattn_fwd_int8qk")
+            need = _lib.lib.miniattn_fwd_balanced_scratch_bytes(C.byref(p)) if balance else 0
+            if need < 0:
+                _lib.check(int(need), "miniattn_fwd_balanced_scratch_bytes")
+            if need > 0:
+                scratch = _scratch_for(q.device, stream, int(need))
+                rc = _lib.lib.miniattn_fwd_int8qk_balanced(C.byref(p8), C.c_void_p(scratch.data_ptr()),
+                                                           C.c_size_t(scratch.numel()), C.c_void_p(stream))
+            else:
+                rc = _lib.lib.miniattn_fwd_int8qk(C.byref(p8), C.c_void_p(stream))
+            _lib.check(rc, "miniattn_fwd_int8qk")
     return (out, lse) if return_lse else out
 
 

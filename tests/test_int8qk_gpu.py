@@ -82,3 +82,28 @@ def test_config4_full_size():
     assert cosine(out[:, :, rows], ref) >= 0.999
     fp16 = miniattn.flash_attn_fwd(q.to(DEV), k.to(DEV), v.to(DEV)).cpu()
     assert cosine(out, fp16) >= 0.999
+
+
+@pytest.mark.parametrize("D,causal", [(64, False), (128, True)])
+def test_int8qk_balanced_launch_matches_plain_launch(D, causal):
+    """Few, long work items: the planner cuts their key ranges; the INT8-QK kernel must give the
+    same result (up to the fp32 order of the merge) through miniattn_fwd_int8qk_balanced."""
+    from miniattn.ops import plan_info
+    B, H, N = 1, 2, 4096
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert plan_info(B, H, N, N, D, causal=causal, sm_count=sms)[0].n_cut_items > 0
+    q, k, v = config4_inputs(B, H, N, D, torch.float16, seed=11)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    buf = miniattn.Int8QK(B, H, H, N, N, D, DEV)
+    plain, lse_p = miniattn.flash_attn_fwd_int8qk(qd, kd, vd, causal=causal, return_lse=True, buffers=buf,
+                                                  balance=False)
+    bal, lse_b = miniattn.flash_attn_fwd_int8qk(qd, kd, vd, causal=causal, return_lse=True, buffers=buf,
+                                                quantize=False, balance=True)
+    torch.cuda.synchronize()
+    assert miniattn.device_status(DEV) == 0
+    assert (bal.float() - plain.float()).abs().max().item() <= 5e-4
+    # the int8 exponent is formed as x*c - (bias*c + m) in one FMA: the rounding of that constant
+    # (about 3e-5 in log2 units) changes with the running maximum, which differs between pieces
+    assert (lse_b - lse_p).abs().max().item() <= 1e-4
+    ref = attention_reference(q, k, v, causal=causal, out_dtype=torch.float32)
+    assert cosine(bal.cpu(), ref) >= 0.999
