@@ -59,7 +59,7 @@ SWEEP_N = (512, 1024, 2048, 4096)
 METRIC = "attention fwd TFLOPS (fp16, D=128, N=512-8192) and % of B200 dense peak"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of fwd_ws_kernel from the ncu capture
 # summarised under profiles/ (workload key -> bytes); None until a capture exists.
-NCU_TRAFFIC_BYTES = {"c2": 294.6e6, "c4": 109.9e6}
+NCU_TRAFFIC_BYTES = {"c2": 293.9e6, "c4": 109.9e6}
 
 
 def flops(B, H, N, D, causal):
