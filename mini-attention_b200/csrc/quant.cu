@@ -89,6 +89,19 @@ __device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long 
   constexpr int PER = 16 * D / 256;  // chunks per thread (128 rows * D/8 chunks / 256 threads)
   __shared__ float mean[D];
   __shared__ float wmax[8];
+  const uint16_t* base = x + b * sb + h * sh;
+  // The slab stays in registers as loaded (16-bit pairs) and is unpacked twice, once for the
+  // maximum and once for the quantisation: a quarter of the registers of an fp32 copy, so more
+  // CTAs (and bytes in flight) fit an SM.  The loads are issued before the channel means are
+  // summed, so that the two global-memory latencies overlap.
+  uint4 raw[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int id = threadIdx.x + i * 256;
+    const int row = blk * 128 + id / CPR, col8 = id % CPR;
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (row < N) raw[i] = *reinterpret_cast<const uint4*>(base + row * sn + col8 * 8);
+  }
   if (SMOOTH) {
     if (threadIdx.x < D) {
       float s = 0.f;
@@ -100,24 +113,19 @@ __device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long 
     }
     __syncthreads();
   }
-  const uint16_t* base = x + b * sb + h * sh;
-  float v[PER][8];
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int id = threadIdx.x + i * 256;
     const int row = blk * 128 + id / CPR, col8 = id % CPR;
     if (row < N) {
-      const uint4 w = *reinterpret_cast<const uint4*>(base + row * sn + col8 * 8);
-      unpack8<BF16>(w, v[i]);
+      float f[8];
+      unpack8<BF16>(raw[i], f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        if (SMOOTH) v[i][e] -= mean[col8 * 8 + e];
-        amax = fmaxf(amax, fabsf(v[i][e]));
+        if (SMOOTH) f[e] -= mean[col8 * 8 + e];
+        amax = fmaxf(amax, fabsf(f[e]));
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
     }
   }
 #pragma unroll
@@ -136,10 +144,13 @@ __device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long 
     const int id = threadIdx.x + i * 256;
     const int row = blk * 128 + id / CPR, col8 = id % CPR;
     if (row < N) {
+      float f[8];
+      unpack8<BF16>(raw[i], f);
       uint32_t lo = 0, hi = 0;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        int qv = __float2int_rn(__fdiv_rn(v[i][e], scale));
+        if (SMOOTH) f[e] -= mean[col8 * 8 + e];
+        int qv = __float2int_rn(__fdiv_rn(f[e], scale));
         qv = max(-127, min(127, qv));
         if (e < 4) lo |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * e);
         else hi |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * (e - 4));
