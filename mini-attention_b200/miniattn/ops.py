@@ -284,10 +284,35 @@ class HostPipeline:
         self.s_out = torch.cuda.Stream(self.device)
         self.ev_in = [torch.cuda.Event() for _ in self.chunks]
         self.ev_done = [torch.cuda.Event() for _ in self.chunks]
+        self._launches: dict = {}  # (causal, scale, kernel) -> per-chunk parameter blocks, filled once
+
+    def _params(self, causal, softmax_scale, kernel):
+        """Parameter blocks of the chunk launches: the staging tensors never move, so the blocks
+        (and the scratch size of the balanced launch) are built once per (causal, scale, kernel)."""
+        key = (bool(causal), softmax_scale, kernel)
+        entry = self._launches.get(key)
+        if entry is None:
+            G = self.G
+            blocks, need = [], 0
+            for b, h0, h1 in self.chunks:
+                p, _, _ = _prepare(self.qd[b:b + 1, h0 * G:h1 * G], self.kd[b:b + 1, h0:h1], self.vd[b:b + 1, h0:h1],
+                                   causal, softmax_scale, "bhnd", False, self.od[b:b + 1, h0 * G:h1 * G], kernel, 0, 0)
+                n = _lib.lib.miniattn_fwd_balanced_scratch_bytes(C.byref(p))
+                if n < 0:
+                    _lib.check(int(n), "miniattn_fwd_balanced_scratch_bytes")
+                need = max(need, int(n))
+                blocks.append(p)
+            entry = self._launches[key] = (blocks, need)
+        return entry
 
     def __call__(self, q, k, v, out, *, causal=False, softmax_scale=None, kernel="auto"):
         G = self.G
         main = torch.cuda.current_stream(self.device)
+        blocks, need = self._params(causal, softmax_scale, kernel)
+        scratch = _scratch_for(self.device, main.cuda_stream, need) if need > 0 else None
+        sptr = C.c_void_p(scratch.data_ptr()) if scratch is not None else None
+        ssize = C.c_size_t(scratch.numel() if scratch is not None else 0)
+        stream = C.c_void_p(main.cuda_stream)
         self.s_in.wait_stream(main)   # staging buffers may still be in use by earlier work
         self.s_out.wait_stream(main)
         for i, (b, h0, h1) in enumerate(self.chunks):
@@ -297,9 +322,7 @@ class HostPipeline:
                 self.vd[b, h0:h1].copy_(v[b, h0:h1], non_blocking=True)
                 self.ev_in[i].record(self.s_in)
             main.wait_event(self.ev_in[i])
-            flash_attn_fwd(self.qd[b:b + 1, h0 * G:h1 * G], self.kd[b:b + 1, h0:h1], self.vd[b:b + 1, h0:h1],
-                           causal=causal, softmax_scale=softmax_scale, kernel=kernel,
-                           out=self.od[b:b + 1, h0 * G:h1 * G])
+            _lib.check(_lib.lib.miniattn_fwd_balanced(C.byref(blocks[i]), sptr, ssize, stream), "miniattn_fwd_balanced")
             self.ev_done[i].record(main)
             self.s_out.wait_event(self.ev_done[i])
             with torch.cuda.stream(self.s_out):
