@@ -34,23 +34,27 @@ def test_version_string():
     assert "sm_100a" in miniattn.version()
 
 
-def test_params_layout_matches_c(tmp_path):
-    """Compile the header as plain C and compare sizeof/offsetof with the ctypes mirror."""
+def test_struct_layouts_match_c(tmp_path):
+    """Compile the header as plain C and compare sizeof/offsetof of every struct with its ctypes mirror."""
     from miniattn import _lib
-    fields = [f[0] for f in _lib.FwdParams._fields_]
+    pairs = [("MiniAttnFwdParams", _lib.FwdParams), ("MiniAttnInt8Params", _lib.Int8Params),
+             ("MiniAttnMergeParams", _lib.MergeParams), ("MiniAttnPlanInfo", _lib.PlanInfo),
+             ("MiniAttnPlanPiece", _lib.PlanPiece)]
     src = tmp_path / "layout.c"
-    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){",
-             'printf("%zu\\n", sizeof(MiniAttnFwdParams));']
-    for f in fields:
-        lines.append(f'printf("%zu\\n", offsetof(MiniAttnFwdParams, {f}));')
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
+    for cname, mirror in pairs:
+        lines.append(f'printf("%zu\\n", sizeof({cname}));')
+        for f in mirror._fields_:
+            lines.append(f'printf("%zu\\n", offsetof({cname}, {f[0]}));')
     lines.append("return 0;}")
     src.write_text("\n".join(lines))
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", str(src), "-o", str(exe)], check=True)
-    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
-    assert int(out[0]) == C.sizeof(_lib.FwdParams)
-    for f, off in zip(fields, out[1:]):
-        assert int(off) == getattr(_lib.FwdParams, f).offset, f
+    out = iter(subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split())
+    for cname, mirror in pairs:
+        assert int(next(out)) == C.sizeof(mirror), cname
+        for f in mirror._fields_:
+            assert int(next(out)) == getattr(mirror, f[0]).offset, (cname, f[0])
 
 
 def _params(**kw):
