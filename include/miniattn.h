@@ -54,6 +54,22 @@ extern "C" {
  * Strides are in ELEMENTS for the logical dims (batch, head, token); the head
  * dim is contiguous (stride 1).  Every stride must be a multiple of 8 elements
  * and every base pointer 16-byte aligned (TMA tensor-map rules).
+ *
+ * Head dim D: 64, 96 or 128 (the reference instantiates 128 only,
+ * flash_attention.cu:77-80).  D = 96 runs on the D = 128 kernels with the
+ * columns 96..127 of every tile zero-filled / clipped by the tensor maps.
+ *
+ * Carried state (ring / context-parallel steps; no reference counterpart, the
+ * arithmetic is the split-KV merge of
+ * kernels/standard/pytorch/benchmark_mla_decode_torch.py:257-266 kept
+ * un-normalised): a sequence of calls over the SAME q and successive key blocks
+ * can hand the rows' running (maximum, sum, un-normalised O) from call to call
+ * in `carry`, a device buffer of miniattn_fwd_carry_bytes(p) bytes, 256-byte
+ * aligned, whose layout is private to the library.  First call: carry_in = 0,
+ * carry_out = 1; middle calls: both 1; last call: carry_in = 1, carry_out = 0 —
+ * only that one writes o (and lse).  While carry_out = 1 nothing is written to
+ * o, which may then be NULL.  Nothing is rounded to 16 bit between the calls.
+ * Calls with carried state always take the plain launch.
  */
 typedef struct MiniAttnFwdParams {
   const void* q;          /* [B, Hq,  Nq, D] logical, device memory                */
@@ -74,10 +90,16 @@ typedef struct MiniAttnFwdParams {
   float   softmax_scale;  /* <= 0 selects 1/sqrt(D) (the reference's fixed scale,  */
                           /* forward_kernel.cuh:103-105)                           */
   int32_t kernel;         /* MINIATTN_KERNEL_*                                     */
+  void*   carry;          /* running state of the rows between ring steps, or NULL */
+  int32_t carry_in;       /* 1: fold the state in `carry` into this call's result  */
+  int32_t carry_out;      /* 1: store the new state in `carry`, write no output    */
 } MiniAttnFwdParams;
 
 /* Launch the forward kernel on `stream` (a cudaStream_t; NULL = default stream). */
 int miniattn_fwd(const MiniAttnFwdParams* p, void* stream);
+
+/* Bytes of the `carry` buffer for the q of `p` (B, Hq, Nq, D are read); negative MINIATTN_E* on error. */
+int64_t miniattn_fwd_carry_bytes(const MiniAttnFwdParams* p);
 
 /*
  * Balanced forward launch (no counterpart in the reference, which launches one CTA per (batch,

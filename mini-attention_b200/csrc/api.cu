@@ -45,9 +45,6 @@ cudaError_t launch_merge_partials(float* acc_o, float* acc_lse, const void* part
 namespace {
 
 thread_local char g_err[512] = "";
-#ifdef MA_TRACE
-unsigned long long* g_trace = nullptr;
-#endif
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -118,18 +115,24 @@ int device_sm_count(int* sms, int* major) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(MINIATTN_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-  static int cached_dev = -1, cached_sms = 0, cached_major = 0;
-  if (cached_dev != dev) {
-    cudaDeviceProp prop;
-    e = cudaGetDeviceProperties(&prop, dev);
-    if (e != cudaSuccess)
-      return fail(MINIATTN_ECUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
-    cached_dev = dev;
-    cached_sms = prop.multiProcessorCount;
-    cached_major = prop.major;
+  // one entry per device ordinal, filled on first use under a lock (host threads may drive
+  // different devices at the same time)
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int table_sms[kMaxDevices] = {0};
+  static int table_major[kMaxDevices] = {0};
+  if (dev < 0 || dev >= kMaxDevices) return fail(MINIATTN_EUNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> g(mu);
+  if (table_sms[dev] == 0) {
+    int n = 0, mj = 0;
+    if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&mj, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+      return fail(MINIATTN_ECUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+    table_sms[dev] = n;
+    table_major[dev] = mj;
   }
-  *sms = cached_sms;
-  *major = cached_major;
+  *sms = table_sms[dev];
+  *major = table_major[dev];
   return MINIATTN_OK;
 }
 
@@ -137,7 +140,12 @@ int device_sm_count(int* sms, int* major) {
 
 extern "C" {
 
-const char* miniattn_version(void) { return "miniattn-b200 0.1 sm_100a"; }
+const char* miniattn_version(void) { return "miniattn-b200 0.2 sm_100a"; }
+
+// Head dim the kernels are instantiated for.  D = 96 runs on the D = 128 kernels: the tensor maps
+// carry the true extent, so TMA zero-fills columns 96..127 of every Q, K and V tile on the way in
+// (zeros change neither Q K^T nor P V) and clips them from the O tile on the way out.
+static int kernel_head_dim(int D) { return D == 96 ? 128 : D; }
 
 const char* miniattn_last_error_string(void) { return g_err; }
 
@@ -146,8 +154,8 @@ static int check_fwd_params(const MiniAttnFwdParams* p) {
   if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
   if (p->dtype != MINIATTN_FP16 && p->dtype != MINIATTN_BF16)
     return fail(MINIATTN_EUNSUPPORTED, "dtype must be fp16 (0) or bf16 (1), got %d", p->dtype);
-  if (p->D != 64 && p->D != 128)
-    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64 or 128)", p->D);
+  if (p->D != 64 && p->D != 96 && p->D != 128)
+    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64, 96 or 128)", p->D);
   if (p->B < 0 || p->Hq < 0 || p->Hkv < 0 || p->Nq < 0 || p->Nk < 0)
     return fail(MINIATTN_EINVAL, "negative size");
   if (p->B == 0 || p->Hq == 0 || p->Nq == 0) return 1;  // empty output: nothing to do
@@ -158,9 +166,20 @@ static int check_fwd_params(const MiniAttnFwdParams* p) {
   if (p->causal != 0 && p->causal != 1) return fail(MINIATTN_EINVAL, "causal must be 0 or 1");
   if (p->kernel < MINIATTN_KERNEL_AUTO || p->kernel > MINIATTN_KERNEL_WS)
     return fail(MINIATTN_EINVAL, "unknown kernel selector %d", p->kernel);
+  if ((p->carry_in != 0 && p->carry_in != 1) || (p->carry_out != 0 && p->carry_out != 1))
+    return fail(MINIATTN_EINVAL, "carry_in and carry_out must be 0 or 1");
+  const bool carry = p->carry_in || p->carry_out;
+  if (carry) {
+    if (p->carry == nullptr) return fail(MINIATTN_EINVAL, "carry_in / carry_out set but carry is null");
+    if (reinterpret_cast<uintptr_t>(p->carry) % 256 != 0)
+      return fail(MINIATTN_EINVAL, "carry must be 256-byte aligned");
+    if (p->kernel == MINIATTN_KERNEL_SIMPLE)
+      return fail(MINIATTN_EUNSUPPORTED, "the carried state needs the warp-specialised kernel");
+  }
   int rc;
   if ((rc = check_tensor(p->q, p->q_stride, p->D, "q")) != 0) return rc;
-  if ((rc = check_tensor(p->o, p->o_stride, p->D, "o")) != 0) return rc;
+  // a call that only stores the running state writes no output: o may be null then
+  if (!(p->carry_out && p->o == nullptr) && (rc = check_tensor(p->o, p->o_stride, p->D, "o")) != 0) return rc;
   // With no keys every row is fully masked; K/V pointers are still handed to the tensor-map
   // encoder, so they must be valid whenever Nk > 0.
   const bool has_keys = p->Nk > 0;
@@ -189,13 +208,12 @@ static void fill_args(const MiniAttnFwdParams* p, ma::FwdArgs* a) {
   a->n_pair_items = 0;  // set by the warp-specialised launcher
   a->sq = nullptr;
   a->sk = nullptr;
-  a->trace = nullptr;
   a->part_o = nullptr;
   a->part_ml = nullptr;
   a->counters = nullptr;
-#ifdef MA_TRACE
-  a->trace = g_trace;
-#endif
+  a->carry_o = nullptr;
+  a->carry_ml = nullptr;
+  a->carry_mode = 0;
 }
 
 static int check_device(int* sms) {
@@ -293,27 +311,39 @@ static int fwd_common(const MiniAttnFwdParams* p, void* scratch, size_t scratch_
     tm[1] = tm[0];
     tm[2] = tm[0];
   }
-  if ((rc = make_map(&tm[3], p->o, 2, dt, p->D, p->Nq, p->Hq, p->B, p->o_stride, ma::kBoxCols,
-                     ma::kTileM, "o")) != 0)
+  if (p->o == nullptr) {
+    tm[3] = tm[0];  // state-only call: the kernel never stores through the output map
+  } else if ((rc = make_map(&tm[3], p->o, 2, dt, p->D, p->Nq, p->Hq, p->B, p->o_stride, ma::kBoxCols,
+                            ma::kTileM, "o")) != 0) {
     return rc;
+  }
 
   ma::FwdArgs a;
   fill_args(p, &a);
+  const int kd = kernel_head_dim(p->D);
+  const bool carry = p->carry_in || p->carry_out;
+  if (carry) {
+    const size_t rows = static_cast<size_t>(p->B) * p->Hq * a.n_q_tiles * ma::kTileM;
+    a.carry_o = static_cast<float*>(p->carry);
+    a.carry_ml = reinterpret_cast<float2*>(static_cast<uint8_t*>(p->carry) + rows * kd * sizeof(float));
+    a.carry_mode = (p->carry_in ? 1 : 0) | (p->carry_out ? 2 : 0);
+  }
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int kernel = p->kernel;
   if (kernel == MINIATTN_KERNEL_AUTO) kernel = MINIATTN_KERNEL_WS;
   cudaError_t e;
   if (kernel == MINIATTN_KERNEL_SIMPLE) {
-    e = ma::launch_fwd_simple(p->D, p->dtype == MINIATTN_BF16, tm, a, st);
+    e = ma::launch_fwd_simple(kd, p->dtype == MINIATTN_BF16, tm, a, st);
   } else {
+    // a call that carries ring state always takes the plain launch
     std::shared_ptr<const ma::FwdPlan> plan;
-    if (scratch != nullptr && has_keys) plan = cached_plan(a, p->D, sms);
+    if (scratch != nullptr && has_keys && !carry) plan = cached_plan(a, kd, sms);
     if (plan && plan->split) {
-      if ((rc = bind_scratch(*plan, p->D, scratch, scratch_bytes, &a)) != 0) return rc;
-      e = ma::launch_fwd_ws_plan(p->D, p->dtype == MINIATTN_BF16, false, tm, a, *plan, st);
+      if ((rc = bind_scratch(*plan, kd, scratch, scratch_bytes, &a)) != 0) return rc;
+      e = ma::launch_fwd_ws_plan(kd, p->dtype == MINIATTN_BF16, false, tm, a, *plan, st);
     } else {
-      e = ma::launch_fwd_ws(p->D, p->dtype == MINIATTN_BF16, tm, a, sms, st);
+      e = ma::launch_fwd_ws(kd, p->dtype == MINIATTN_BF16, tm, a, sms, st);
     }
   }
   if (e != cudaSuccess)
@@ -338,8 +368,8 @@ int miniattn_plan_fwd(const MiniAttnFwdParams* p, int sm_count, MiniAttnPlanInfo
   if (info == nullptr) return fail(MINIATTN_EINVAL, "info is null");
   memset(info, 0, sizeof(*info));
   if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
-  if (p->D != 64 && p->D != 128)
-    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64 or 128)", p->D);
+  if (p->D != 64 && p->D != 96 && p->D != 128)
+    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64, 96 or 128)", p->D);
   if (p->B < 0 || p->Hq < 0 || p->Nq < 0 || p->Nk < 0) return fail(MINIATTN_EINVAL, "negative size");
   if (p->Hq > 65535 || p->B > 65535)
     return fail(MINIATTN_EUNSUPPORTED, "B and Hq must not exceed 65535");
@@ -354,9 +384,10 @@ int miniattn_plan_fwd(const MiniAttnFwdParams* p, int sm_count, MiniAttnPlanInfo
   info->sm_count = sms;
   info->n_ctas = n_items;
   if (p->B == 0 || p->Hq == 0 || p->Nq == 0 || p->Nk == 0 ||
-      (p->kernel != MINIATTN_KERNEL_AUTO && p->kernel != MINIATTN_KERNEL_WS))
+      (p->kernel != MINIATTN_KERNEL_AUTO && p->kernel != MINIATTN_KERNEL_WS) || p->carry_in || p->carry_out)
     return MINIATTN_OK;
-  std::shared_ptr<const ma::FwdPlan> plan = cached_plan(a, p->D, sms);
+  const int kd = kernel_head_dim(p->D);
+  std::shared_ptr<const ma::FwdPlan> plan = cached_plan(a, kd, sms);
   info->est_plain = plan->est_plain;
   info->est_balanced = plan->est_balanced;
   if (!plan->split) return MINIATTN_OK;
@@ -366,7 +397,7 @@ int miniattn_plan_fwd(const MiniAttnFwdParams* p, int sm_count, MiniAttnPlanInfo
   info->n_ctas = plan->n_whole + plan->n_table;
   info->n_cut_items = plan->n_cut_items;
   info->n_slots = plan->n_slots;
-  info->scratch_bytes = static_cast<int64_t>(scratch_bytes_of(*plan, p->D));
+  info->scratch_bytes = static_cast<int64_t>(scratch_bytes_of(*plan, kd));
   if (pieces != nullptr)
     for (int k = 0; k < plan->n_table && k < cap; ++k) {
       const ma::PlanEntry& e = plan->table.e[k];
@@ -378,6 +409,16 @@ int miniattn_plan_fwd(const MiniAttnFwdParams* p, int sm_count, MiniAttnPlanInfo
       pieces[k].slot = e.nparts > 1 ? e.slot0 + e.part : -1;
     }
   return MINIATTN_OK;
+}
+
+int64_t miniattn_fwd_carry_bytes(const MiniAttnFwdParams* p) {
+  g_err[0] = 0;
+  if (p == nullptr) return fail(MINIATTN_EINVAL, "params is null");
+  if (p->D != 64 && p->D != 96 && p->D != 128)
+    return fail(MINIATTN_EUNSUPPORTED, "head dim %d not supported (64, 96 or 128)", p->D);
+  if (p->B < 0 || p->Hq < 0 || p->Nq < 0) return fail(MINIATTN_EINVAL, "negative size");
+  const int64_t tiles = static_cast<int64_t>(p->B) * p->Hq * ((p->Nq + ma::kTileM - 1) / ma::kTileM);
+  return tiles * ma::kTileM * (kernel_head_dim(p->D) * 4 + 8);
 }
 
 int64_t miniattn_fwd_balanced_scratch_bytes(const MiniAttnFwdParams* p) {
@@ -399,6 +440,9 @@ static int check_int8_params(const MiniAttnInt8Params* p, bool need_v) {
   }
   int rc = check_fwd_params(&f);
   if (rc != 0) return rc;
+  if (p->fwd.D == 96) return fail(MINIATTN_EUNSUPPORTED, "the INT8-QK variant takes head dim 64 or 128");
+  if (p->fwd.carry_in || p->fwd.carry_out)
+    return fail(MINIATTN_EUNSUPPORTED, "the INT8-QK variant does not carry ring state");
   if (p->fwd.Nk == 0) return fail(MINIATTN_EINVAL, "the INT8-QK variant needs at least one key");
   if (!p->q8 || !p->k8 || !p->q_scale || !p->k_scale)
     return fail(MINIATTN_EINVAL, "q8, k8, q_scale and k_scale must not be null");
@@ -541,10 +585,6 @@ int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream) {
     return fail(MINIATTN_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return MINIATTN_OK;
 }
-
-#ifdef MA_TRACE
-void miniattn_debug_set_trace(unsigned long long* p) { g_trace = p; }
-#endif
 
 int miniattn_selftest_wait(int32_t* status, uint64_t limit_ns, void* stream) {
   g_err[0] = 0;

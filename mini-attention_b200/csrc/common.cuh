@@ -20,12 +20,15 @@ struct FwdArgs {
                        // the CTAs after them one Q tile each (the tail of the last wave)
   const float* sq;     // INT8-QK: [B, Hq,  ceil(Nq/128)] Q scales (softmax scale * log2e folded in)
   const float* sk;     // INT8-QK: [B, Hkv, ceil(Nk/128)] K scales
-  unsigned long long* trace;  // debug builds only (MA_TRACE): per-role clock stamps of CTA 0
   // Balanced launches only (null otherwise): where CTAs that cover part of an item's key range
   // leave their partial result, and the per-item arrival counters (zero between launches).
   float*  part_o;      // [slot][2 tiles][D/4][128 rows][4] fp32, un-normalised O of a piece
   float2* part_ml;     // [slot][2 tiles][128 rows]: (row maximum in log2 units, row sum)
   int*    counters;    // [cut item][2 tiles][arrived, published]
+  // Ring steps only (carry_mode != 0): the rows' running state between launches.
+  float*  carry_o;     // [B*Hq*n_q_tiles][D/4][128 rows][4] fp32, un-normalised O
+  float2* carry_ml;    // [B*Hq*n_q_tiles][128 rows]: (row maximum in log2 units, row sum)
+  int     carry_mode;  // bit 0: fold the stored state in; bit 1: store the new state, no output
 };
 
 // One CTA of a balanced launch, read from the launch's table (kernel parameter space).

@@ -28,7 +28,6 @@
 // The row maximum is updated lazily: a row keeps exponentiating against a stale maximum until the
 // true maximum has grown by more than 2^8 (in the exp2 domain), so the O accumulator is rescaled
 // only rarely; l is accumulated against the same maximum, which keeps O / l exact.
-#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -43,11 +42,9 @@ constexpr int kHalfN = kTileN / 2;      // keys per half tile
 constexpr float kLazyThreshold = 8.0f;  // log2 units
 // Register split per thread after setmaxnreg (8 softmax + 4 correction + 4 other warps;
 // 8*176 + 4*88 + 4*72 = 2048 = the 64 K registers of an SM divided by 32 lanes).
-#ifndef MA_REG_SOFTMAX
-#define MA_REG_SOFTMAX 176
-#define MA_REG_CORR 88
-#define MA_REG_OTHER 72
-#endif
+constexpr int kRegSoftmax = 176;
+constexpr int kRegCorr = 88;
+constexpr int kRegOther = 72;
 
 template <int D>
 struct WsLayout {
@@ -68,8 +65,8 @@ struct WsLayout {
   static constexpr int kBarAlpha = kBarPReady + 4;         // [2][2] softmax -> correction
   static constexpr int kBarOReady = kBarAlpha + 4;         // [2][2] correction -> MMA
   static constexpr int kBarODone = kBarOReady + 4;         // [2][2] MMA -> correction
-  static constexpr int kBarLReady = kBarODone + 4;         // [2]    softmax -> correction (final l)
-  static constexpr int kNumBars = kBarLReady + 2;
+  static constexpr int kBarStagger = kBarODone + 4;        // one-shot: tile 0 published its first row maxima
+  static constexpr int kNumBars = kBarStagger + 1;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem slot, abort flag, arrival order [2]
   static constexpr int kBytes = kOffMisc + 32;
   static constexpr int kDynSmem = kBytes + 1024;
@@ -90,23 +87,6 @@ template <int N>
 __device__ __forceinline__ void reg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
-#ifndef MA_TRACE_SOFTMAX
-#define MA_TRACE_SOFTMAX 1
-#endif
-#ifndef MA_TRACE_CTA
-#define MA_TRACE_CTA 0
-#endif
-#ifdef MA_TRACE
-constexpr int kTraceMax = 2048;
-#define MA_STAMP(role, tag)                                                              \
-  do {                                                                                   \
-    if (a.trace != nullptr && blockIdx.x == MA_TRACE_CTA && trace_n < kTraceMax)         \
-      a.trace[(role) * kTraceMax + trace_n++] =                                          \
-          (static_cast<unsigned long long>(tag) << 48) | (clock64() & 0xFFFFFFFFFFFFull); \
-  } while (0)
-#else
-#define MA_STAMP(role, tag) do {} while (0)
-#endif
 __device__ __forceinline__ void warp_arrive(uint32_t bar) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
@@ -123,7 +103,12 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar) {
 // (row maximum, row sum) in scratch memory, count themselves in on the item's arrival counter, and
 // the one that arrives last folds the others' partials into its own and writes the output; nobody
 // waits for another CTA.
-template <int D, bool BF16, bool QK8, bool PLAN>
+//
+// CARRY: ring (context-parallel) steps.  The rows' running state over the key blocks seen so far
+// -- un-normalised O (fp32, the layout of a balanced launch's partial) and (row maximum, row sum)
+// -- lives in global memory between launches.  With a.carry_mode bit 0 the epilogue folds that state
+// into this launch's result; with bit 1 it writes the new state instead of the 16-bit output.
+template <int D, bool BF16, bool QK8, bool PLAN, bool CARRY = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -144,11 +129,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + L::kOffMisc + 8);
   volatile int* arrival = reinterpret_cast<volatile int*>(gbase + L::kOffMisc + 16);  // [2 tiles]
 
-#ifdef MA_TRACE
-  const long long trace_entry = clock64();
-  // per-CTA record after the stamp area: (SM id, global timer at entry, at exit)
-  const unsigned long long trace_t0 = global_timer_ns();
-#endif
   const int tid = threadIdx.x;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler
   const int lane = tid & 31;
@@ -238,6 +218,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       uint32_t count = 1;  // Q full, K/V full, S full, O done: one arrival (a TMA or MMA commit)
       if (i >= L::kBarKvEmpty && i < L::kBarSFull) count = nt;      // one release per issuing thread
       else if (i >= L::kBarPReady && i < L::kBarODone) count = 4;   // P ready, alpha, O ready: 4 warps
+      else if (i == L::kBarStagger) count = 4;                      // the 4 softmax warps of tile 0, once
       mbar_init(bar(i), count);
     }
     if (lane == 0) *abort_flag = 0;
@@ -264,22 +245,14 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
   const WaitCtx wc{abort_flag, a.status, MINIATTN_WAIT_LIMIT_NS};
   const float c = a.scale_log2;
-#ifdef MA_TRACE
-  int trace_n = 0;
-#endif
 
   if (warp < 8) {
     // =========================== softmax ===========================================
-    reg_inc<MA_REG_SOFTMAX>();
+    reg_inc<kRegSoftmax>();
     const int t = warp >> 2;
     if (t < nt) {
       const int r = tid & 127;
       const int row = q0 + t * kTileM + r;
-#ifdef MA_TRACE
-      if (r == 0 && a.trace != nullptr && blockIdx.x == MA_TRACE_CTA)
-        a.trace[t * kTraceMax + trace_n++] = (18ull << 48) | (trace_entry & 0xFFFFFFFFFFFFull);
-#endif
-      if (r == 0) MA_STAMP(t, 19);
       const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
       const uint32_t tS = tmem_base + L::kColS + 128 * t + lane_off;
       long long vis_ll = a.Nk;
@@ -308,12 +281,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int hb = 0; hb < 2; ++hb) {
           mbar_wait(bar(L::kBarSFull + 2 * t + hb), j & 1, wc, kErrWaitS);
           tc_fence_after();
-          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 1);
           uint32_t s[2][32];
           tmem_ld32(tS + hb * kHalfN, s[0]);
           tmem_ld32(tS + hb * kHalfN + 32, s[1]);
           tmem_wait_ld();
-          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 2);
           if constexpr (QK8) {
             // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding the
             // bit pattern of 1.5*2^23 gives the float 12582912 + acc exactly.  The offset stays in:
@@ -358,7 +329,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
           alpha_smem[(2 * t + hb) * kTileM + r] = alpha;
           warp_arrive(bar(L::kBarAlpha + 2 * t + hb));
-          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 3);
+          if (t == 0 && j == 0 && hb == 0) warp_arrive(bar(L::kBarStagger));
 
           // exponent of a score x: x*cj - m; for the int8 variant x carries kBias, taken out here
           float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
@@ -380,11 +351,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tmem_wait_st();
           tc_fence_before();
           warp_arrive(bar(L::kBarPReady + 2 * t + hb));
-          if (MA_TRACE_SOFTMAX && r == 0) MA_STAMP(t, 4);
         }
       }
 
-      if ((!PLAN || pe_nparts == 1) && a.lse != nullptr && row < a.Nq) {
+      if ((!PLAN || pe_nparts == 1) && !(CARRY && a.carry_mode != 0) && a.lse != nullptr && row < a.Nq) {
         const float lse = (l_run > 0.f) ? (m_cur * 0.6931471805599453f + __logf(l_run)) : -INFINITY;
         a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] = lse;
       }
@@ -393,7 +363,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         mbar_wait(bar(L::kBarODone + 2 * t + 1), (n_tiles - 1) & 1, wc, kErrWaitO);
         tc_fence_after();
       }
-      if (r == 0) MA_STAMP(t, 20);
       // A CTA that covers a piece of an item's key range publishes its partial result; the last
       // piece to arrive folds the other pieces into its own accumulator and writes the output.
       float f_self = (l_run > 0.f) ? (1.f / l_run) : 0.f;  // factor of this CTA's own accumulator
@@ -408,7 +377,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           int* cnt = a.counters + 4 * pe_counter + 2 * t;  // [0] arrived, [1] published
           if (r == 0) arrival[t] = atomicAdd(cnt, 1);
           named_bar_sync(kBarEpilogue + t, 128);
-          if (r == 0) MA_STAMP(t, 21);
           write_out = (arrival[t] == pe_nparts - 1);
           if (!write_out) {
             const long long my = (static_cast<long long>(pe_slot0 + pe_part) * 2 + t) * kTileM;
@@ -427,18 +395,20 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             a.part_ml[my + r] = make_float2(m_cur, l_run);
             __threadfence();
             named_bar_sync(kBarEpilogue + t, 128);
-            if (r == 0) atomicAdd(cnt + 1, 1);
-            if (r == 0) MA_STAMP(t, 22);
+            if (r == 0) {
+              __threadfence();  // release: the group's stores (ordered by the barrier) before the count
+              atomicAdd(cnt + 1, 1);
+            }
           } else {
             // Every other piece has counted in, so it is publishing right now or has finished:
             // a short, bounded wait for the last of them, then the counters go back to zero.
             if (r == 0) {
               count_wait(cnt + 1, pe_nparts - 1, wc, kErrWaitPeer);
+              __threadfence();  // acquire side: nothing below is read before the count was seen
               cnt[0] = 0;
               cnt[1] = 0;
             }
             named_bar_sync(kBarEpilogue + t, 128);
-            if (r == 0) MA_STAMP(t, 23);
             __threadfence();
             // The other pieces' partials come in through the K/V ring (this tile's half of it),
             // one bulk copy each; the ring is free once the other Q tile's MMAs are done too.
@@ -472,7 +442,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             }
             const float mt = (m_tot == -INFINITY) ? 0.f : m_tot;
             const float inv_l = (l_tot > 0.f) ? (1.f / l_tot) : 0.f;
-            if (r == 0) MA_STAMP(t, 24);
             if (a.lse != nullptr && row < a.Nq)
               a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] =
                   (l_tot > 0.f) ? (m_tot * 0.6931471805599453f + __logf(l_tot)) : -INFINITY;
@@ -487,7 +456,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               const float wp = ex2(m_p - mt);
               mbar_wait(bar(L::kBarQFull + t), phase, wc, kErrWaitKV);
               phase ^= 1;
-              if (r == 0) MA_STAMP(t, 25);
               if (p == last_other) {  // folded in while the output is written, below
                 f_part = wp * inv_l;
                 break;
@@ -518,6 +486,74 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
         }
       }
+      if constexpr (CARRY) {
+        if (a.carry_mode != 0) {
+          const long long tix =
+              (static_cast<long long>(b) * a.Hq + h) * a.n_q_tiles + (q0 / kTileM + t);
+          float* c_o = a.carry_o + tix * kTileM * D;
+          float2* c_ml = a.carry_ml + tix * kTileM;
+          constexpr uint32_t kPartBytes = D * kTileM * 4;
+          const uint32_t ring_off = L::kOffRing + t * (L::kStages / 2) * L::kTileBytes;
+          float m_tot = m_cur, l_tot = l_run, w_self = 1.f, w_c = 0.f;
+          if (a.carry_mode & 1) {
+            // The state comes in through this tile's half of the K/V ring, idle once the other
+            // Q tile's MMAs are done too.
+            if (n_tiles > 0 && nt == 2)
+              mbar_wait(bar(L::kBarODone + 2 * (1 - t) + 1), (n_tiles - 1) & 1, wc, kErrWaitO);
+            if (r == 0) {
+              fence_proxy_async_all();
+              mbar_expect_tx(bar(L::kBarQFull + t), kPartBytes);
+              bulk_load(sbase + ring_off, c_o, kPartBytes, bar(L::kBarQFull + t));
+            }
+            const float2 ml = __ldcg(c_ml + r);
+            m_tot = fmaxf(m_cur, ml.x);
+            const float mt = (m_tot == -INFINITY) ? 0.f : m_tot;
+            w_self = ex2(m_cur - mt);
+            w_c = ex2(ml.x - mt);
+            l_tot = l_run * w_self + ml.y * w_c;
+            // the tile's Q barrier completed phase 0 with the Q load (issued only when there are keys)
+            mbar_wait(bar(L::kBarQFull + t), n_tiles > 0 ? 1u : 0u, wc, kErrWaitKV);
+            s_part = reinterpret_cast<const float4*>(gbase + ring_off) + r;
+          }
+          if (a.carry_mode & 2) {
+            // new state: O relative to the merged maximum, still un-normalised
+            write_out = false;
+            float4* po = reinterpret_cast<float4*>(c_o) + r;
+#pragma unroll
+            for (int q = 0; q < D / 32; ++q) {
+              uint32_t o[32];
+              if (n_tiles > 0) {
+                tmem_ld32(tO + q * 32, o);
+                tmem_wait_ld();
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = 0u;
+              }
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                float4 x = make_float4(__uint_as_float(o[4 * g]) * w_self, __uint_as_float(o[4 * g + 1]) * w_self,
+                                       __uint_as_float(o[4 * g + 2]) * w_self, __uint_as_float(o[4 * g + 3]) * w_self);
+                if (s_part != nullptr) {
+                  const float4 y = s_part[(q * 8 + g) * kTileM];
+                  x.x = fmaf(y.x, w_c, x.x);
+                  x.y = fmaf(y.y, w_c, x.y);
+                  x.z = fmaf(y.z, w_c, x.z);
+                  x.w = fmaf(y.w, w_c, x.w);
+                }
+                po[(q * 8 + g) * kTileM] = x;
+              }
+            }
+            c_ml[r] = make_float2(m_tot, l_tot);
+          } else {
+            const float inv_l = (l_tot > 0.f) ? (1.f / l_tot) : 0.f;
+            f_self = w_self * inv_l;
+            f_part = w_c * inv_l;
+            if (a.lse != nullptr && row < a.Nq)
+              a.lse[(static_cast<long long>(b) * a.Hq + h) * a.Nq + row] =
+                  (l_tot > 0.f) ? (m_tot * 0.6931471805599453f + __logf(l_tot)) : -INFINITY;
+          }
+        }
+      }
       if (write_out) {
         // ---- epilogue of this Q tile (the two softmax groups run theirs side by side):
         //      O / l -> 16 bit -> swizzled smem (the tile's Q buffer) -> TMA store
@@ -535,7 +571,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = 0.f;
           }
-          if constexpr (PLAN) {
+          if constexpr (PLAN || CARRY) {
             if (s_part != nullptr) {
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
@@ -565,20 +601,18 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         fence_proxy_async_smem();
         named_bar_sync(kBarEpilogue + t, 128);
         if (r == 0) {
-          MA_STAMP(t, 26);
 #pragma unroll
           for (int bx = 0; bx < L::kBoxes; ++bx)
             tma_store_4d(&tm_o, stage + bx * kBoxBytes, bx * kBoxCols, q0 + t * kTileM, h, b);
           tma_store_commit();
           tma_store_wait_read0();  // the staging buffer must outlive the copy's reads, no more
-          MA_STAMP(t, 27);
         }
       }
       tc_fence_before();
     }
   } else if (warp < 12) {
     // =========================== correction ========================================
-    reg_dec<MA_REG_CORR>();
+    reg_dec<kRegCorr>();
     const int r = tid & 127;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     for (int j = 0; j < n_tiles; ++j) {
@@ -611,7 +645,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
     tc_fence_before();
   } else {
-    reg_dec<MA_REG_OTHER>();
+    reg_dec<kRegOther>();
     if (warp == 12 || warp == 14) {
       // =========================== MMA issuers =====================================
       // One issuing thread per Q tile (warp 12 -> tile 0, warp 14 -> tile 1).  Each walks its
@@ -656,9 +690,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         int cons = 0;  // ring consumption index: K_0, V_0, K_1, V_1, ...
         mbar_wait(bar(L::kBarKvFull + 0), 0, wc, kErrWaitKV);
         // Start tile 1 about half a softmax step after tile 0 (when tile 0 has published its
-        // first P): the two softmax groups then alternate between their max and exp2 phases
-        // instead of competing for the exp2 unit at the same moments.
-        if (t == 1) mbar_wait(bar(L::kBarAlpha + 0), 0, wc, kErrWaitP);
+        // first row maxima): the two softmax groups then alternate between their max and exp2
+        // phases instead of competing for the exp2 unit at the same moments.  The barrier
+        // completes exactly once, so a late issuer can never mistake a later phase for it.
+        if (t == 1) mbar_wait(bar(L::kBarStagger), 0, wc, kErrWaitP);
         tc_fence_after();
         for (int hb = 0; hb < 2; ++hb) {
           issue_s(hb, 0);
@@ -675,11 +710,9 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const uint32_t kpar = (cons / L::kStages) & 1;
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
-            MA_STAMP(3 + t, 10 + hb);
             mbar_wait(bar(L::kBarOReady + 2 * t + hb), j & 1, wc, kErrWaitCorr);
             mbar_wait(bar(L::kBarPReady + 2 * t + hb), j & 1, wc, kErrWaitP);
             tc_fence_after();
-            MA_STAMP(3 + t, 14 + hb);
             const uint32_t tP = tSt + kHalfN * hb;
 #pragma unroll
             for (int kk = 0; kk < kHalfN / 16; ++kk) {
@@ -699,7 +732,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               mma_commit(bar(L::kBarSFull + 2 * t + hb));
               if (hb == 1) mma_commit(bar(L::kBarKvEmpty + kslot));
             }
-            MA_STAMP(3 + t, 18 + hb);
           }
           if (has_next) ++cons;
         }
@@ -732,23 +764,13 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem_base, L::kTmemCols);
   }
-#ifdef MA_TRACE
-  if (tid == 0 && a.trace != nullptr) {
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    unsigned long long* rec = a.trace + 5 * kTraceMax + 3ull * blockIdx.x;
-    rec[0] = smid;
-    rec[1] = trace_t0;
-    rec[2] = global_timer_ns();
-  }
-#endif
 }
 
 // ---------------------------------------------------------------------------------
-template <int D, bool BF16, bool QK8>
+template <int D, bool BF16, bool QK8, bool CARRY = false>
 static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_count, cudaStream_t st) {
   using L = WsLayout<D>;
-  auto kern = fwd_ws_kernel<D, BF16, QK8, false>;
+  auto kern = fwd_ws_kernel<D, BF16, QK8, false, CARRY>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
   if (e != cudaSuccess) return e;
@@ -767,8 +789,7 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_c
   long long grid = items;
   const long long rest = sm_count > 0 ? items % sm_count : 0;
   const long long kv_tiles = (a.Nk + kTileN - 1) / kTileN;
-  static const bool no_split = getenv("MINIATTN_NO_TAIL_SPLIT") != nullptr;  // A/B switch for measurements
-  if (!no_split && items > sm_count && rest > 0 && 2 * rest <= sm_count && (a.n_q_tiles % 2) == 0 && kv_tiles >= 8) {
+  if (items > sm_count && rest > 0 && 2 * rest <= sm_count && (a.n_q_tiles % 2) == 0 && kv_tiles >= 8) {
     args.n_pair_items = static_cast<int>(items - rest);
     grid = items + rest;
   }
@@ -809,6 +830,15 @@ cudaError_t launch_fwd_ws_plan(int D, bool bf16, bool qk8, const CUtensorMap* tm
 
 cudaError_t launch_fwd_ws(int D, bool bf16, const CUtensorMap* tm, const FwdArgs& a, int sm_count,
                           cudaStream_t st) {
+  if (a.carry_mode != 0) {  // a ring step: running state in, state or output out
+    if (D == 128)
+      return bf16 ? launch_ws_t<128, true, false, true>(tm, a, sm_count, st)
+                  : launch_ws_t<128, false, false, true>(tm, a, sm_count, st);
+    if (D == 64)
+      return bf16 ? launch_ws_t<64, true, false, true>(tm, a, sm_count, st)
+                  : launch_ws_t<64, false, false, true>(tm, a, sm_count, st);
+    return cudaErrorInvalidValue;
+  }
   if (D == 128)
     return bf16 ? launch_ws_t<128, true, false>(tm, a, sm_count, st) : launch_ws_t<128, false, false>(tm, a, sm_count, st);
   if (D == 64)

@@ -29,6 +29,7 @@ class FwdParams(C.Structure):
         ("Nq", C.c_int32), ("Nk", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("causal", C.c_int32),
         ("softmax_scale", C.c_float), ("kernel", C.c_int32),
+        ("carry", C.c_void_p), ("carry_in", C.c_int32), ("carry_out", C.c_int32),
     ]
 
 
@@ -84,6 +85,8 @@ def _load() -> C.CDLL:
     lib.miniattn_fwd_balanced.restype = C.c_int
     lib.miniattn_fwd_balanced_scratch_bytes.argtypes = [C.POINTER(FwdParams)]
     lib.miniattn_fwd_balanced_scratch_bytes.restype = C.c_int64
+    lib.miniattn_fwd_carry_bytes.argtypes = [C.POINTER(FwdParams)]
+    lib.miniattn_fwd_carry_bytes.restype = C.c_int64
     lib.miniattn_plan_fwd.argtypes = [C.POINTER(FwdParams), C.c_int, C.POINTER(PlanInfo),
                                       C.POINTER(PlanPiece), C.c_int32]
     lib.miniattn_plan_fwd.restype = C.c_int

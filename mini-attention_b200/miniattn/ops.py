@@ -86,9 +86,10 @@ def _bhnd_shape(t: torch.Tensor, layout: str) -> Tuple[int, int, int, int]:
     return b, h, n, d
 
 
-def _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0):
+def _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0, need_out=True):
     """Validate like the reference launcher and fill a FwdParams block.  Returns
-    (params or None when the problem is empty, out, lse)."""
+    (params or None when the problem is empty, out, lse).  ``need_out=False``: a call that only
+    stores carried state; no output tensor is allocated."""
     if layout not in ("bhnd", "bnhd"):
         raise RuntimeError(f"layout must be 'bhnd' or 'bnhd', got {layout!r}")
     if kernel not in _lib.KERNELS:
@@ -115,23 +116,25 @@ def _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_
     if Hkv == 0 or Hq % max(Hkv, 1) != 0:
         raise RuntimeError(f"number of query heads ({Hq}) must be a multiple of KV heads ({Hkv})")
     if out is None:
-        out = torch.empty_like(q)
+        if need_out:
+            out = torch.empty_like(q)
     else:
         if out.shape != q.shape or out.dtype != q.dtype or out.device != q.device:
             raise RuntimeError("out must match q in shape, dtype and device")
         if out.stride(-1) != 1 and out.numel() > 0:
             raise RuntimeError("out must be contiguous in the head dimension")
-    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device) if return_lse else None
+    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device) if return_lse and need_out else None
     if q.numel() == 0:
         return None, out, lse
     p = _lib.FwdParams()
-    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    p.o = out.data_ptr() if out is not None else None
     p.lse = lse.data_ptr() if lse is not None else None
     p.status = _status_word(q.device).data_ptr()
     p.q_stride[:] = _bhn_strides(q, layout)
     p.k_stride[:] = _bhn_strides(k, layout)
     p.v_stride[:] = _bhn_strides(v, layout)
-    p.o_stride[:] = _bhn_strides(out, layout)
+    p.o_stride[:] = _bhn_strides(out if out is not None else q, layout)
     p.q_pos0, p.k_pos0 = int(q_pos0), int(k_pos0)
     p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D = B, Hq, Hkv, Nq, Nk, D
     p.dtype = _DTYPES[q.dtype]
@@ -155,6 +158,9 @@ def flash_attn_fwd(
     q_pos0: int = 0,
     k_pos0: int = 0,
     balance: bool = True,
+    carry: Optional[torch.Tensor] = None,
+    carry_in: bool = False,
+    carry_out: bool = False,
 ):
     """O = softmax(Q K^T * scale [+ causal mask]) V on the GPU.
 
@@ -168,12 +174,28 @@ def flash_attn_fwd(
     ``miniattn_fwd_balanced``: when the work items do not fill a whole number of rounds of one CTA
     per SM, the key range of some items is cut over several CTAs inside the one launch (scratch for
     their partial results is cached per device and stream).
+
+    ``carry`` (a buffer from :func:`carry_state`) chains calls over the same q and successive key
+    blocks, as the ring launcher does: with ``carry_out`` the rows' running (maximum, sum,
+    un-normalised O) are stored in it and nothing is returned; with ``carry_in`` the stored state is
+    folded into this call's result.  The last call of a chain (``carry_in`` only) returns the output.
     """
-    p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0)
+    use_carry = bool(carry_in or carry_out)
+    if use_carry and carry is None:
+        raise RuntimeError("carry_in / carry_out need a carry buffer (carry_state)")
+    p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0,
+                           need_out=not carry_out)
+    if p is not None and use_carry:
+        need_c = _lib.lib.miniattn_fwd_carry_bytes(C.byref(p))
+        if need_c < 0:
+            _lib.check(int(need_c), "miniattn_fwd_carry_bytes")
+        if not carry.is_cuda or carry.device != q.device or carry.numel() * carry.element_size() < need_c:
+            raise RuntimeError(f"carry must be a CUDA buffer on q's device of at least {need_c} bytes")
+        p.carry, p.carry_in, p.carry_out = carry.data_ptr(), int(bool(carry_in)), int(bool(carry_out))
     if p is not None:
         with torch.cuda.device(q.device):
             stream = torch.cuda.current_stream(q.device).cuda_stream
-            need = _lib.lib.miniattn_fwd_balanced_scratch_bytes(C.byref(p)) if balance else 0
+            need = _lib.lib.miniattn_fwd_balanced_scratch_bytes(C.byref(p)) if balance and not use_carry else 0
             if need < 0:
                 _lib.check(int(need), "miniattn_fwd_balanced_scratch_bytes")
             if need > 0:
@@ -183,7 +205,22 @@ def flash_attn_fwd(
             else:
                 rc = _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
         _lib.check(rc, "miniattn_fwd")
+    if carry_out:
+        return None
     return (out, lse) if return_lse else out
+
+
+def carry_state(q: torch.Tensor, layout: str = "bhnd") -> torch.Tensor:
+    """Device buffer for the running state of q's rows across a chain of ``flash_attn_fwd`` calls
+    (``carry=...``).  Its layout is private to the library; its content is defined only between a
+    ``carry_out`` call and the ``carry_in`` call that follows."""
+    B, Hq, Nq, D = _bhnd_shape(q, layout)
+    p = _lib.FwdParams()
+    p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D = B, Hq, Hq, Nq, Nq, D
+    n = _lib.lib.miniattn_fwd_carry_bytes(C.byref(p))
+    if n < 0:
+        _lib.check(int(n), "miniattn_fwd_carry_bytes")
+    return torch.empty(max(int(n), 256), dtype=torch.uint8, device=q.device)
 
 
 class Int8QK:

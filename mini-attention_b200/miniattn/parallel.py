@@ -9,9 +9,13 @@ The reference has no multi-GPU code; these launchers add the two modes the path 
 * **ring (context-parallel) mode** — for sequences too long for one device.  The sequence is cut
   into 2*W blocks; rank r owns query/key/value blocks r and 2W-1-r ("zig-zag"), which balances
   causal work.  The K/V pair of each rank travels round the ring (send to r+1, receive from r-1)
-  while the attention of the resident Q blocks against the visiting pair runs; each step yields a
-  normalised partial and its log-sum-exp, merged with the running result (the split-KV merge of
-  kernels/standard/pytorch/benchmark_mla_decode_torch.py:244-272).
+  while the attention of the resident Q blocks against the visiting pair runs.  The rows' running
+  (maximum, sum, un-normalised O) are carried from one attention launch to the next inside the
+  kernel's epilogue (the split-KV merge of
+  kernels/standard/pytorch/benchmark_mla_decode_torch.py:244-272, kept un-normalised until the
+  last step), so a step is one launch per (Q block, K/V block) pair and nothing is rounded to
+  16 bit on the way.  The two-launch form (normalised partial + log-sum-exp, merged by
+  ``miniattn_merge_partials``) stays available: ``fused=False``.
 
 The schedule functions are pure Python and are exercised on CPU ranks (gloo) in the tests; the
 attention and merge callables are injectable so that the same driver runs on the CUDA kernels
@@ -147,10 +151,11 @@ def ring_forward(
     rank: int = 0,
     world: int = 1,
     group=None,
-    attn_fn: Callable = _gpu_attn,
-    accumulator: Callable = _GpuAccumulator,
+    attn_fn: Optional[Callable] = None,
+    accumulator: Optional[Callable] = None,
     exchange: Optional[Callable] = None,
     verify_origin: bool = False,
+    fused: bool = True,
 ) -> torch.Tensor:
     """Ring / context-parallel attention of this rank's zig-zag shard.
 
@@ -162,17 +167,27 @@ def ring_forward(
     the transfer of step s+1 overlaps the attention of step s.  With ``verify_origin`` the
     handle's ``origin()`` (rank the received pair started from) is compared with the schedule and
     a dropped or repeated hop raises ``RuntimeError`` (host-side check; it synchronises, so it is
-    meant for tests and debugging).
+    meant for tests and debugging).  ``attn_fn`` / ``accumulator`` replace the CUDA kernels (CPU
+    stand-ins in the tests); with neither given and ``fused`` the running state is carried inside
+    the attention kernel, otherwise each task yields a partial that the accumulator merges.
     """
     B, H, L2, D = q_local.shape
     L = L2 // 2
+    fused = fused and attn_fn is None and accumulator is None
+    attn_fn = attn_fn or _gpu_attn
+    accumulator = accumulator or _GpuAccumulator
     if exchange is None and world > 1:
         exchange = _dist_exchange(rank, world, group)
     k_cur, v_cur = k_local.contiguous(), v_local.contiguous()
     bufs = [(torch.empty_like(k_cur), torch.empty_like(v_cur)) for _ in range(2 if world > 1 else 0)]
     q_blocks = (q_local[:, :, :L], q_local[:, :, L:])
-    accs = [accumulator(q_blocks[0]), accumulator(q_blocks[1])]
     out = torch.empty_like(q_local)
+    if fused:
+        from .ops import carry_state, flash_attn_fwd
+        states = [carry_state(q_blocks[0]), carry_state(q_blocks[1])]
+        started = [False, False]
+    else:
+        accs = [accumulator(q_blocks[0]), accumulator(q_blocks[1])]
     outs = (out[:, :, :L], out[:, :, L:])
     # number of partials each resident block will receive, to know which merge is the last one
     remaining = [0, 0]
@@ -187,9 +202,18 @@ def ring_forward(
         for t in ring_step_tasks(rank, world, s, causal):
             kb = k_cur[:, :, t.kv_half * L:(t.kv_half + 1) * L]
             vb = v_cur[:, :, t.kv_half * L:(t.kv_half + 1) * L]
-            o, lse = attn_fn(q_blocks[t.q_half], kb, vb, t.causal, t.q_block * L, t.kv_block * L, softmax_scale)
             remaining[t.q_half] -= 1
             last = remaining[t.q_half] == 0
+            if fused:
+                # one launch: state in (after the block's first task), state out or, on the block's
+                # last task, the finished rows straight into the output
+                flash_attn_fwd(q_blocks[t.q_half], kb, vb, causal=t.causal, q_pos0=t.q_block * L,
+                               k_pos0=t.kv_block * L, softmax_scale=softmax_scale,
+                               out=outs[t.q_half] if last else None, carry=states[t.q_half],
+                               carry_in=started[t.q_half], carry_out=not last)
+                started[t.q_half] = True
+                continue
+            o, lse = attn_fn(q_blocks[t.q_half], kb, vb, t.causal, t.q_block * L, t.kv_block * L, softmax_scale)
             # the last merge of a block writes the finished rows straight into the output
             accs[t.q_half].add(o, lse, out=outs[t.q_half] if last else None)
         if handle is not None:
@@ -239,8 +263,8 @@ def _dist_exchange(rank: int, world: int, group):
     return exchange
 
 
-def ring_forward_emulated(q, k, v, world: int, *, causal=True, softmax_scale=None, attn_fn=_gpu_attn,
-                          accumulator=_GpuAccumulator) -> torch.Tensor:
+def ring_forward_emulated(q, k, v, world: int, *, causal=True, softmax_scale=None, attn_fn=None,
+                          accumulator=None, fused=True) -> torch.Tensor:
     """All `world` ranks of the ring run one after another in this process (no communication):
     the same schedule, kernels and merges as :func:`ring_forward`, for single-device checks."""
     qs, ks, vs = zigzag_split(q, world), zigzag_split(k, world), zigzag_split(v, world)
@@ -261,5 +285,6 @@ def ring_forward_emulated(q, k, v, world: int, *, causal=True, softmax_scale=Non
             return _Done()
 
         outs.append(ring_forward(qs[r], ks[r], vs[r], causal=causal, softmax_scale=softmax_scale, rank=r,
-                                 world=world, attn_fn=attn_fn, accumulator=accumulator, exchange=exchange))
+                                 world=world, attn_fn=attn_fn, accumulator=accumulator, exchange=exchange,
+                                 fused=fused))
     return zigzag_merge(outs)

@@ -76,7 +76,11 @@ def _params(**kw):
     "kw, code, text",
     [
         (dict(dtype=7), -2, "dtype"),
-        (dict(D=96), -2, "head dim"),
+        (dict(D=80), -2, "head dim"),
+        (dict(carry_in=1), -1, "carry is null"),
+        (dict(carry_out=1, carry=0x1010), -1, "256-byte aligned"),
+        (dict(carry_out=1, carry=0x1000, kernel=1), -2, "warp-specialised"),
+        (dict(carry_in=3, carry=0x1000), -1, "0 or 1"),
         (dict(Nq=-1), -1, "negative"),
         (dict(Hkv=3), -1, "multiple of Hkv"),
         (dict(causal=2), -1, "causal"),

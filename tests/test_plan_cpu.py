@@ -142,7 +142,7 @@ def test_plan_entry_rejects_bad_arguments():
     import ctypes as C
     from miniattn import _lib
     p = _lib.FwdParams()
-    p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D = 1, 1, 1, 128, 128, 96
+    p.B, p.Hq, p.Hkv, p.Nq, p.Nk, p.D = 1, 1, 1, 128, 128, 80
     info = _lib.PlanInfo()
     assert _lib.lib.miniattn_plan_fwd(C.byref(p), 148, C.byref(info), None, 0) == _lib.EUNSUPPORTED
     p.D = 128
