@@ -154,6 +154,18 @@ def main(ref_root: Path) -> None:
             y, weights = mod(x, mask=mask)
             core = weights @ v  # exactly the `output = weights @ v` line of MHA.forward
             _save(f"mha_core_{tag}", q=q, k=k, v=v, out=core, weights=weights, causal=int(mask is not None))
+        # the module end to end (projections included): input, parameters, both return values
+        torch.manual_seed(6)
+        small = mha.MHA(d_model=128, n_heads=2)
+        xs = torch.randn(1, 64, 128)
+        sd = {name.replace(".", "__"): t for name, t in small.state_dict().items()}
+        res = {}
+        for tag, mask in (("full", None), ("masked", torch.tril(torch.ones(64, 64)))):
+            res[f"y_{tag}"], res[f"weights_{tag}"] = small(xs, mask=mask)
+        # an all-ones mask hides nothing (mask == 0 -> -inf, mha.py:43-44): same result as no mask
+        y1, w1 = small(xs, mask=torch.ones(64, 64))
+        res["ones_equals_full"] = int(torch.equal(y1, res["y_full"]) and torch.equal(w1, res["weights_full"]))
+        _save("mha_module", x=xs, **res, **sd)
 
 
 def kernel_config_strings(ref_root: Path) -> None:

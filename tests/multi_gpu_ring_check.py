@@ -7,7 +7,7 @@ Every rank builds the same seeded full tensors, keeps its zig-zag shard, runs th
 compares its rows with the single-launch kernel on the full sequence (and rank 0 additionally with
 the CPU oracle on sampled rows).  Shard mode: every rank computes its (batch x KV-head) units and
 the all-gathered result is compared with the full computation.  Prints one line per rank and exits
-non-zero on a mismatch.  (Not collected by pytest: it needs more than one GPU.)
+non-zero on a mismatch.  tests/test_parallel_gpu.py launches it when the box has two GPUs or more.
 """
 import argparse
 import os
@@ -44,6 +44,9 @@ def main():
         qs, ks, vs = (par.zigzag_split(t, world)[rank].contiguous() for t in (q, k, v))
         out = par.ring_forward(qs, ks, vs, causal=True, rank=rank, world=world, verify_origin=True)
         err = (out.float() - par.zigzag_split(full, world)[rank].float()).abs().max().item()
+        # the two-launch form (16-bit partials + merge kernel) over the same ring
+        out2 = par.ring_forward(qs, ks, vs, causal=True, rank=rank, world=world, fused=False)
+        err = max(err, (out2.float() - par.zigzag_split(full, world)[rank].float()).abs().max().item())
         line = f"rank {rank}/{world} ring {dtype}: max|ring - single| = {err:.3e}"
         if rank == 0:
             from oracle.attention_oracle import attention_reference_rows

@@ -70,3 +70,22 @@ def test_mha_core(name):
     if g["causal"]:
         w = torch.tril(w)
     assert (w - g["weights"]).abs().max().item() <= 1e-5
+
+
+def test_mha_module_end_to_end():
+    """The reference MHA module run whole (projections, masked softmax, both return values):
+    the oracle reproduces its output and its weights from the stored parameters."""
+    g = load_golden("mha_module")
+    assert g["ones_equals_full"] == 1
+    x = g["x"]
+    H, dh = 2, 64
+    lin = lambda n: x @ g[f"{n}__weight"].t() + g[f"{n}__bias"]  # noqa: E731
+    q, k, v = (lin(n).view(1, 64, H, dh).transpose(1, 2) for n in ("w_q", "w_k", "w_v"))
+    for tag, causal in (("full", False), ("masked", True)):
+        o, lse = attention_reference(q, k, v, causal=causal, return_lse=True)
+        y = o.transpose(1, 2).reshape(1, 64, H * dh) @ g["w_o__weight"].t() + g["w_o__bias"]
+        assert (y - g[f"y_{tag}"]).abs().max().item() <= 1e-5
+        w = torch.exp((q @ k.transpose(-1, -2)) / math.sqrt(dh) - lse.unsqueeze(-1))
+        if causal:
+            w = torch.tril(w)
+        assert (w - g[f"weights_{tag}"]).abs().max().item() <= 1e-5

@@ -1,6 +1,13 @@
-"""Merge kernel and launchers on one GPU: the merge kernel against the oracle's merge, the ring
-driver with all ranks emulated on the device (same schedule, kernels and merges as the
-multi-process ring, no communication) and shard mode run rank after rank."""
+"""Merge kernel and launchers: the merge kernel against the oracle's merge, the ring driver with
+all ranks emulated on one device (same schedule, kernels and merges as the multi-process ring, no
+communication), config 5 at its full size against the row-sampled oracle, shard mode run rank
+after rank, and -- where the box has two GPUs or more -- the real NCCL ring and shard launchers
+as one process per GPU."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
 import pytest
 import torch
 
@@ -42,14 +49,16 @@ def test_merge_kernel_matches_oracle(dtype, D):
     assert torch.equal(a_o.cpu(), part_o.float()) and torch.equal(a_l.cpu(), part_lse)
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
-def test_ring_emulated_on_gpu_scaled_down_config5(world):
+def test_ring_emulated_on_gpu_scaled_down_config5(world, fused):
     """Config 5 scaled to N=8192 (B=1, H=4, D=128, fp16, causal): the ring result must agree
-    with the single-launch kernel and with the exact oracle on sampled rows."""
+    with the single-launch kernel and with the exact oracle on sampled rows.  fused: the running
+    state is carried inside the attention kernel; otherwise 16-bit partials + the merge kernel."""
     N = 8192
     q, k, v = make_inputs(1, 4, 4, N, N, 128, torch.float16, seed=5)
     qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
-    out = par.ring_forward_emulated(qd, kd, vd, world, causal=True).cpu()
+    out = par.ring_forward_emulated(qd, kd, vd, world, causal=True, fused=fused).cpu()
     single = miniattn.flash_attn_fwd(qd, kd, vd, causal=True).cpu()
     assert miniattn.device_status(DEV) == 0
     assert (out.float() - single.float()).abs().max().item() <= TOL[torch.float16]
@@ -60,11 +69,60 @@ def test_ring_emulated_on_gpu_scaled_down_config5(world):
     assert (out[:, :, rows].float() - ref).abs().max().item() <= TOL[torch.float16]
 
 
-def test_ring_emulated_non_causal_bf16_gqa():
+@pytest.mark.parametrize("fused", [True, False])
+def test_ring_emulated_non_causal_bf16_gqa(fused):
     q, k, v = make_inputs(1, 4, 2, 2048, 2048, 64, torch.bfloat16, seed=8)
-    out = par.ring_forward_emulated(q.to(DEV), k.to(DEV), v.to(DEV), 4, causal=False).cpu()
+    out = par.ring_forward_emulated(q.to(DEV), k.to(DEV), v.to(DEV), 4, causal=False, fused=fused).cpu()
     ref = attention_reference(q, k, v, out_dtype=torch.float32)
     assert (out.float() - ref).abs().max().item() <= TOL[torch.bfloat16]
+
+
+def test_config5_full_size_rows():
+    """Config 5 at its stated size -- causal MHA fp16, B=1, H=32, N=131072, D=128 -- through the
+    ring schedule of 8 ranks (zig-zag blocks of L=8192 tokens, every rank's steps run one after
+    the other on this device).  The full oracle is out of reach on a CPU (64 GiB of scores per
+    head), so 288 query rows per head are computed exactly against all their keys: row 0, every
+    block boundary and its two neighbours, N-1, and seeded random rows.  Bar: 2e-3."""
+    B, H, N, D, W = 1, 32, 131072, 128, 8
+    L = N // (2 * W)
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(B, H, N, D, generator=g, dtype=torch.float32).half()
+    k = torch.randn(B, H, N, D, generator=g, dtype=torch.float32).half()
+    v = torch.randn(B, H, N, D, generator=g, dtype=torch.float32).half()
+    out = par.ring_forward_emulated(q.to(DEV), k.to(DEV), v.to(DEV), W, causal=True)
+    assert miniattn.device_status(DEV) == 0
+    rows = {0, N - 1}
+    for blk in range(1, 2 * W):
+        rows |= {blk * L - 1, blk * L, blk * L + 1}
+    extra = torch.randint(0, N, (512,), generator=torch.Generator().manual_seed(5)).tolist()
+    for r in extra:
+        if len(rows) >= 288:
+            break
+        rows.add(r)
+    rows = torch.tensor(sorted(rows))
+    assert rows.numel() >= 256
+    got = out[:, :, rows.to(DEV)].float().cpu()
+    del out
+    ref = attention_reference_rows(q, k, v, rows, causal=True)
+    assert (got - ref).abs().max().item() <= TOL[torch.float16]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs or more (one process per GPU)")
+def test_nccl_ring_and_shards_multi_process():
+    """The real thing: one process per GPU, K/V pairs over NCCL send/recv, origin tags verified,
+    ring output against the single-launch kernel and the CPU oracle, shard mode all-reduced
+    against the full computation (tests/multi_gpu_ring_check.py prints a line per rank)."""
+    n = min(torch.cuda.device_count(), 8)
+    n = 1 << (n.bit_length() - 1)   # 2, 4 or 8 ranks
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29517",
+           str(root / "tests" / "multi_gpu_ring_check.py"), "--seq-len", "16384"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900, env=env)
+    print(r.stdout[-4000:])
+    assert r.returncode == 0, r.stdout[-4000:]
+    assert "multi-GPU check passed" in r.stdout
 
 
 def test_shard_mode_rank_by_rank():

@@ -237,12 +237,30 @@ def test_variant_modules_match_reference_math():
         o = attention_reference(q.half(), kk.half(), vv.half(), causal=True, out_dtype=torch.float32)
         y_ref = mod.w_o(o.transpose(1, 2).reshape(2, 256, 512))
         assert maxerr(y, y_ref.detach()) <= 2e-2
-    mha = miniattn.MHA(512, 4).half().to(DEV)
-    y0 = mha(x.to(DEV))
-    y1 = mha(x.to(DEV), mask=torch.tril(torch.ones(256, 256, device=DEV)))
-    assert y0.shape == y1.shape == (2, 256, 512) and not torch.equal(y0, y1)
-    with pytest.raises(RuntimeError, match="lower-triangular"):
-        mha(x.to(DEV), mask=torch.ones(256, 256, device=DEV))
+
+
+def test_mha_module_against_reference_module():
+    """MHA through the module, against what the reference's own MHA module returned for the same
+    parameters and input (fixture written by tests/golden/make_golden.py): both return values,
+    no mask / lower-triangular mask / all-ones mask; any other mask raises."""
+    g = load_golden("mha_module")
+    mha = miniattn.MHA(128, 2)
+    mha.load_state_dict({k.replace("__", "."): v for k, v in g.items() if k.startswith("w_")})
+    mha = mha.half().to(DEV)
+    x = g["x"].half().to(DEV)
+    S = x.shape[1]
+    tril = torch.tril(torch.ones(S, S, device=DEV))
+    for tag, mask in (("full", None), ("masked", tril), ("full", torch.ones(S, S, device=DEV))):
+        y, w = mha(x, mask=mask)   # the reference's arity: `output, weights = mha(x)`
+        assert y.shape == (1, S, 128) and w.shape == (1, 2, S, S) and w.dtype == x.dtype
+        # fp16 activations and projections against the fp32 module
+        assert maxerr(y.cpu(), g[f"y_{tag}"]) <= 1e-2
+        assert maxerr(w.cpu(), g[f"weights_{tag}"]) <= 2e-3
+    y, w = miniattn.MHA(128, 2, need_weights=False).half().to(DEV)(x)
+    assert w is None and y.shape == (1, S, 128)
+    with pytest.raises(RuntimeError, match="no eager path"):
+        mha(x, mask=torch.triu(torch.ones(S, S, device=DEV)))
+    assert miniattn.device_status(DEV) == 0
 
 
 def test_host_buffer_pipeline():
@@ -298,3 +316,73 @@ def test_last_wave_single_tile_ctas():
             pass
         assert maxerr(out[:, :, rows], ref) <= TOL[torch.float16]
         assert maxerr(out, simple) <= TOL[torch.float16]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("causal", [False, True])
+def test_head_dim_96(dtype, kernel, causal):
+    """D = 96 (the reference instantiates D = 128 only, flash_attention.cu:77-80): ragged lengths,
+    GQA, both kernels, against the oracle; scale defaults to 1/sqrt(96)."""
+    q, k, v = make_inputs(2, 4, 2, 333, 200 if not causal else 333, 96, dtype, seed=96)
+    ref, ref_lse = attention_reference(q, k, v, causal=causal, return_lse=True, out_dtype=torch.float32)
+    out, lse = run(q, k, v, causal=causal, kernel=kernel, return_lse=True)
+    assert out.shape == q.shape and maxerr(out, ref) <= TOL[dtype]
+    assert maxerr(lse, ref_lse) <= 2e-3
+    # (B,N,H,D) layout: token stride 4*96 elements
+    qb, kb, vb = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    outb = run(qb, kb, vb, causal=causal, kernel=kernel, layout="bnhd")
+    assert maxerr(outb.transpose(1, 2), ref) <= TOL[dtype]
+
+
+def test_head_dim_96_balanced_launch():
+    """A D = 96 launch the planner cuts (few long items): partials and merge run at the kernel's
+    padded head dim."""
+    q, k, v = make_inputs(1, 1, 1, 4096, 4096, 96, torch.float16, seed=97)
+    rows = torch.tensor([0, 1, 127, 128, 2047, 2048, 4000, 4095])
+    ref = attention_reference_rows(q, k, v, rows, causal=True)
+    out = run(q, k, v, causal=True)
+    assert maxerr(out[:, :, rows], ref) <= TOL[torch.float16]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D", [64, 96, 128])
+def test_carried_state_chain(dtype, D):
+    """Key blocks fed one call at a time with the rows' running state carried in the library's
+    buffer (carry_out / carry_in): equals the single call over all keys, and the oracle.  Ragged
+    block sizes, GQA, a causal diagonal that hides the later blocks from the early rows."""
+    q, k, v = make_inputs(1, 4, 2, 300, 700, D, dtype, seed=31 + D)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    for causal, q_pos0 in ((False, 0), (True, 100)):
+        ref, ref_lse = attention_reference(q, k, v, causal=causal, q_pos0=q_pos0, return_lse=True,
+                                           out_dtype=torch.float32)
+        single = miniattn.flash_attn_fwd(qd, kd, vd, causal=causal, q_pos0=q_pos0)
+        state = miniattn.carry_state(qd)
+        cuts = [0, 128, 391, 700]   # key blocks [0,128) [128,391) [391,700)
+        res = None
+        for i in range(3):
+            kb, vb = kd[:, :, cuts[i]:cuts[i + 1]], vd[:, :, cuts[i]:cuts[i + 1]]
+            res = miniattn.flash_attn_fwd(qd, kb, vb, causal=causal, q_pos0=q_pos0, k_pos0=cuts[i],
+                                          carry=state, carry_in=i > 0, carry_out=i < 2, return_lse=i == 2)
+            assert (res is None) == (i < 2)
+        out, lse = res
+        assert miniattn.device_status(DEV) == 0
+        assert maxerr(out.cpu(), ref) <= TOL[dtype]
+        assert maxerr(out, single) <= (5e-4 if dtype == torch.float16 else 4e-3)
+        assert maxerr(lse.cpu(), ref_lse) <= 2e-3
+
+
+def test_carried_state_rows_without_keys():
+    """A chain whose first block is entirely in the rows' future (state = nothing seen yet) and a
+    chain that ends on such a block: rows keep what the other blocks gave them."""
+    q, k, v = make_inputs(1, 2, 2, 256, 512, 128, torch.float16, seed=77)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ref = attention_reference(q, k[:, :, :256], v[:, :, :256], causal=True, out_dtype=torch.float32)
+    for order in ((1, 0), (0, 1)):   # block 1 = keys 256..511, hidden from every row
+        state = miniattn.carry_state(qd)
+        out = None
+        for i, blk in enumerate(order):
+            out = miniattn.flash_attn_fwd(qd, kd[:, :, 256 * blk:256 * blk + 256], vd[:, :, 256 * blk:256 * blk + 256],
+                                          causal=True, k_pos0=256 * blk, carry=state, carry_in=i > 0, carry_out=i < 1)
+        assert maxerr(out.cpu(), ref) <= TOL[torch.float16]
+    assert miniattn.device_status(DEV) == 0
