@@ -205,7 +205,11 @@ int miniattn_fwd_int8qk_balanced(const MiniAttnInt8Params* p, void* scratch, siz
  * message naming both numbers.  Results are identical to miniattn_quant_qk_int8.
  *
  * The first call on each device looks up the array's device address (with that device current);
- * make that first call outside any stream capture.  All calls on a device share the one array,
+ * make that first call outside any stream capture.  It is also the moment the CUDA driver loads
+ * this library's device code onto that GPU (module loading is lazy by default), array included —
+ * the one step on this path that takes device memory, a few MB, and that can therefore fail on a
+ * GPU whose memory is already spoken for.  So make the first call on every device at start-up,
+ * BEFORE the host reserves the rest of the memory; a one-tile problem is enough.  All calls on a device share the one array,
  * which keeps whatever the last call left in it: nothing in it needs clearing (every entry that is
  * read is written earlier in the same call), but two calls whose kernels overlap on the GPU —
  * different streams, no ordering between them — race on it.  Keep such calls on one stream or
@@ -245,6 +249,16 @@ int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream);
  * ORs bit 30 into *status (device memory) and the kernel returns normally.
  */
 int miniattn_selftest_wait(int32_t* status, uint64_t limit_ns, void* stream);
+
+/*
+ * Turns a status word read back from the device (MiniAttnFwdParams.status, after synchronising)
+ * into a return code: 0 when it is zero, MINIATTN_EDEVICE_WAIT otherwise, with the bounded waits
+ * that ran out named in miniattn_last_error_string().  After such a failure the outputs of the
+ * launches that shared the word are undefined, and the arrival counters of a balanced launch's
+ * scratch may be non-zero: clear the word and the first 16384 bytes of that scratch before the
+ * next launch.  Host arithmetic only.
+ */
+int miniattn_check_status(int32_t status_word);
 
 /* Library / build identification: "miniattn-b200 <version> sm_100a". */
 const char* miniattn_version(void);

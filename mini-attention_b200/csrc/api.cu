@@ -586,6 +586,24 @@ int miniattn_merge_partials(const MiniAttnMergeParams* p, void* stream) {
   return MINIATTN_OK;
 }
 
+int miniattn_check_status(int32_t status_word) {
+  g_err[0] = 0;
+  if (status_word == 0) return MINIATTN_OK;
+  static const char* const names[] = {"K/V or Q tile load", "S = QK^T", "O += PV", "P hand-off", "ring slot release",
+                                      "correction hand-off", "partial of another CTA of a cut item"};
+  char list[256] = "";
+  for (int bit = 0; bit < 7; ++bit)
+    if (status_word & (1 << bit)) {
+      if (list[0]) strncat(list, ", ", sizeof(list) - strlen(list) - 1);
+      strncat(list, names[bit], sizeof(list) - strlen(list) - 1);
+    }
+  if (status_word & (1 << 30)) {
+    if (list[0]) strncat(list, ", ", sizeof(list) - strlen(list) - 1);
+    strncat(list, "self-test wait", sizeof(list) - strlen(list) - 1);
+  }
+  return fail(MINIATTN_EDEVICE_WAIT, "bounded device waits ran out (status word 0x%x): %s", status_word, list);
+}
+
 int miniattn_selftest_wait(int32_t* status, uint64_t limit_ns, void* stream) {
   g_err[0] = 0;
   if (status == nullptr) return fail(MINIATTN_EINVAL, "status is null");

@@ -99,6 +99,8 @@ def _load() -> C.CDLL:
     lib.miniattn_merge_partials.restype = C.c_int
     lib.miniattn_selftest_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     lib.miniattn_selftest_wait.restype = C.c_int
+    lib.miniattn_check_status.argtypes = [C.c_int32]
+    lib.miniattn_check_status.restype = C.c_int
     lib.miniattn_version.restype = C.c_char_p
     lib.miniattn_last_error_string.restype = C.c_char_p
     return lib

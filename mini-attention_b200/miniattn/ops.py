@@ -45,6 +45,18 @@ def device_status(device: Union[torch.device, str, None] = None) -> int:
     return val
 
 
+def check_device_status(device: Union[torch.device, str, None] = None) -> None:
+    """Synchronise `device` and raise ``RuntimeError`` (MINIATTN_EDEVICE_WAIT, the waits named) if a
+    bounded device-side wait of any launch since the last check ran out.  The operators launch
+    asynchronously and never read the status word themselves, so a caller that wants the check calls
+    this (or :func:`device_status`) where it synchronises anyway; results of the launches in between
+    are undefined when it raises.  The word is cleared and the cached balanced-launch scratch of the
+    device is dropped, so later launches start clean."""
+    val = device_status(device)
+    _lib.check(_lib.lib.miniattn_check_status(C.c_int32(val if val < (1 << 31) else val - (1 << 32))),
+               "device status")
+
+
 def _scratch_for(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     """Scratch of a balanced launch: one buffer per (device, stream), zeroed when created (the
     kernels leave the arrival counters at its start zero again), grown on demand."""
@@ -179,6 +191,10 @@ def flash_attn_fwd(
     blocks, as the ring launcher does: with ``carry_out`` the rows' running (maximum, sum,
     un-normalised O) are stored in it and nothing is returned; with ``carry_in`` the stored state is
     folded into this call's result.  The last call of a chain (``carry_in`` only) returns the output.
+
+    The launch is asynchronous.  Every device-side wait is bounded; one that runs out sets a bit in a
+    per-device status word instead of hanging — poll it with :func:`check_device_status` /
+    :func:`device_status` after synchronising.
     """
     use_carry = bool(carry_in or carry_out)
     if use_carry and carry is None:

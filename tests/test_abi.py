@@ -121,3 +121,18 @@ def test_selftest_rejects_bad_limit():
     from miniattn import _lib
     assert _lib.lib.miniattn_selftest_wait(None, 1000, None) == -1
     assert _lib.lib.miniattn_selftest_wait(0x1000, 0, None) == -1
+
+
+def test_check_status_names_the_waits():
+    from miniattn import _lib
+    assert _lib.lib.miniattn_check_status(0) == 0 and _lib.last_error() == ""
+    assert _lib.lib.miniattn_check_status((1 << 6) | 1) == _lib.EDEVICE_WAIT
+    assert "another CTA" in _lib.last_error() and "tile load" in _lib.last_error()
+    assert _lib.lib.miniattn_check_status(1 << 30) == _lib.EDEVICE_WAIT and "self-test" in _lib.last_error()
+
+
+def test_carry_bytes():
+    from miniattn import _lib
+    p = _params(Nq=300, D=96)          # 3 Q tiles x 2 heads, state kept at the kernel's head dim 128
+    assert _lib.lib.miniattn_fwd_carry_bytes(C.byref(p)) == 1 * 2 * 3 * 128 * (128 * 4 + 8)
+    assert _lib.lib.miniattn_fwd_carry_bytes(C.byref(_params(D=80))) == -2
