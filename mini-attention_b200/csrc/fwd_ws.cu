@@ -46,14 +46,19 @@ constexpr int kRegSoftmax = 176;
 constexpr int kRegCorr = 88;
 constexpr int kRegOther = 72;
 
-template <int D>
+template <int D, bool QK8 = false>
 struct WsLayout {
   static constexpr int kBoxes = D / kBoxCols;
   static constexpr int kTileBytes = kBoxes * kBoxBytes;  // Q, K or V tile (32 KB at D=128)
   static constexpr int kStages = (D == 128) ? 4 : 8;     // ring slots, each one K or V tile
   static constexpr int kOffQ = 0;                        // two Q tiles (reused as O staging)
   static constexpr int kOffRing = 2 * kTileBytes;
-  static constexpr int kOffAlpha = kOffRing + kStages * kTileBytes;  // float[2 tiles][2 halves][128]
+  // INT8-QK only: two constant fp16 operand tiles (A: 128 rows, B: 64 rows, 128-byte swizzled
+  // rows) whose product is 1.5 * 2^23 in every element, see issue_s
+  static constexpr int kOffBiasA = kOffRing + kStages * kTileBytes;
+  static constexpr int kOffBiasB = kOffBiasA + kTileM * 128;
+  static constexpr int kBiasBytes = QK8 ? (kTileM + kTileN / 2) * 128 : 0;
+  static constexpr int kOffAlpha = kOffBiasA + kBiasBytes;           // float[2 tiles][2 halves][128]
   static constexpr int kOffL = kOffAlpha + 2048;                     // float[2][128]
   static constexpr int kOffBar = kOffL + 1024;
   // barrier indices (8 bytes each); [t][h] = index + 2*t + h
@@ -66,13 +71,19 @@ struct WsLayout {
   static constexpr int kBarOReady = kBarAlpha + 4;         // [2][2] correction -> MMA
   static constexpr int kBarODone = kBarOReady + 4;         // [2][2] MMA -> correction
   static constexpr int kBarStagger = kBarODone + 4;        // one-shot: tile 0 published its first row maxima
-  static constexpr int kNumBars = kBarStagger + 1;
+  static constexpr int kBarSFree = kBarStagger + 1;        // [2][2] softmax -> MMA: S half is in registers (D = 64)
+  static constexpr int kNumBars = kBarSFree + 4;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem slot, abort flag, arrival order [2]
   static constexpr int kBytes = kOffMisc + 32;
   static constexpr int kDynSmem = kBytes + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0;     // S buffer of (tile t, half h) at kColS + 128*t + 64*h
   static constexpr int kColO = 256;   // O accumulator of tile t at kColO + D*t
+  // At D = 64 the two O accumulators leave 128 columns free: P gets a region of its own
+  // (tile t, half h at kColP + 64*t + 32*h) instead of overwriting its S buffer, so S_h(j+1) can
+  // be issued as soon as the softmax group holds S_h(j) in registers.
+  static constexpr bool kSepP = false;
+  static constexpr int kColP = 384;
 };
 
 constexpr int kBarEpilogue = 1;  // named barriers 1 and 2: epilogue of softmax group 0 / 1
@@ -114,7 +125,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
               const FwdArgs a,
               const __grid_constant__ std::conditional_t<PLAN, PlanTable, NoPlanTable> plan) {
-  using L = WsLayout<D>;
+  using L = WsLayout<D, QK8>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;
@@ -219,6 +230,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (i >= L::kBarKvEmpty && i < L::kBarSFull) count = nt;      // one release per issuing thread
       else if (i >= L::kBarPReady && i < L::kBarODone) count = 4;   // P ready, alpha, O ready: 4 warps
       else if (i == L::kBarStagger) count = 4;                      // the 4 softmax warps of tile 0, once
+      else if (i >= L::kBarSFree) count = 4;                        // S in registers: 4 warps
       mbar_init(bar(i), count);
     }
     if (lane == 0) *abort_flag = 0;
@@ -238,6 +250,17 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == 12) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), L::kTmemCols);
     tmem_relinquish();
+  }
+  if constexpr (QK8) {
+    // Bias operands: row r of a 128-byte swizzled tile keeps its logical 16-byte chunk 0 at
+    // physical chunk (r & 7); element k = 0 of every row is 3072 (A) or 4096 (B), the rest 0.
+    uint4* bias = reinterpret_cast<uint4*>(gbase + L::kOffBiasA);
+    for (int i = tid; i < L::kBiasBytes / 16; i += kNumThreads) {
+      const int r = i >> 3, chunk = i & 7;
+      const uint32_t v = (r < kTileM) ? 0x6A00u : 0x6C00u;  // fp16 3072.0 / 4096.0
+      bias[i] = make_uint4(chunk == (r & 7) ? v : 0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
   }
   tc_fence_before();
   __syncthreads();
@@ -285,15 +308,14 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tmem_ld32(tS + hb * kHalfN, s[0]);
           tmem_ld32(tS + hb * kHalfN + 32, s[1]);
           tmem_wait_ld();
-          if constexpr (QK8) {
-            // int32 -> fp32 without the conversion pipe: |acc| <= 127*127*D < 2^22, so adding the
-            // bit pattern of 1.5*2^23 gives the float 12582912 + acc exactly.  The offset stays in:
-            // it is order-preserving for the maximum and folds into the constant of the exp2 FMA.
-#pragma unroll
-            for (int q = 0; q < 2; ++q)
-#pragma unroll
-              for (int i = 0; i < 32; ++i) s[q][i] += 0x4B400000u;
+          if constexpr (L::kSepP) {  // the scores are in registers: the MMA role may refill this half
+            tc_fence_before();
+            warp_arrive(bar(L::kBarSFree + 2 * t + hb));
           }
+          // QK8: the accumulator was started at the bit pattern of 1.5*2^23 (see issue_s) and
+          // |acc| <= 127*127*D < 2^22, so the word read here IS the float 12582912 + acc: int32 ->
+          // fp32 with no instruction at all.  The offset stays in: it is order-preserving for the
+          // maximum and folds into the constant of the exp2 FMA.
           const int lim = vis_row - (kv_t0 + j) * kTileN - hb * kHalfN;
           if (lim < kHalfN) {  // diagonal or ragged half: hide the keys this row must not see
 #pragma unroll
@@ -334,20 +356,41 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           // exponent of a score x: x*cj - m; for the int8 variant x carries kBias, taken out here
           float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
           if constexpr (QK8) mc = fmaf(kBias, cj, mc);
-          float psum0 = 0.f, psum1 = 0.f;
+          // two scores per FMA / ADD issue slot (packed f32x2); the exp2 itself is one per lane,
+          // except that one pair in eight is evaluated by a polynomial on the FMA pipe: the exp2
+          // unit (16 results per clock per SM) is co-critical with the tensor pipe, the FMA pipe
+          // has room (larger shares measured slower: the issue slots run out)
+          uint64_t psum = pack_f32x2(0.f, 0.f);
+          const uint64_t cj2 = pack_f32x2(cj, cj), mc2 = pack_f32x2(-mc, -mc);
           uint32_t pk[32];
 #pragma unroll
           for (int q = 0; q < 2; ++q)
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float p0 = ex2(fmaf(__uint_as_float(s[q][i]), cj, -mc));
-              const float p1 = ex2(fmaf(__uint_as_float(s[q][i + 1]), cj, -mc));
-              psum0 += p0;
-              psum1 += p1;
+              float x0, x1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[q][i]), __uint_as_float(s[q][i + 1])), cj2, mc2),
+                           x0, x1);
+              float p0, p1;
+              if ((i & 15) == 0) {
+                exp2_poly_f32x2(x0, x1, p0, p1);
+              } else {
+                p0 = ex2(x0);
+                p1 = ex2(x1);
+              }
+              psum = add_f32x2(psum, pack_f32x2(p0, p1));
               pk[q * 16 + (i >> 1)] = pack2<BF16>(p0, p1);
             }
+          float psum0, psum1;
+          unpack_f32x2(psum, psum0, psum1);
           l_run = l_run * alpha + (psum0 + psum1);
-          tmem_st32(tS + hb * kHalfN, pk);  // P of this half over the first 32 columns of its S
+          if constexpr (L::kSepP) {
+            // P has its own columns; the PV MMA of the previous step must be done reading them
+            if (j > 0) mbar_wait(bar(L::kBarODone + 2 * t + hb), (j - 1) & 1, wc, kErrWaitO);
+            tc_fence_after();
+            tmem_st32(tmem_base + L::kColP + 64 * t + 32 * hb + lane_off, pk);
+          } else {
+            tmem_st32(tS + hb * kHalfN, pk);  // P of this half over the first 32 columns of its S
+          }
           tmem_wait_st();
           tc_fence_before();
           warp_arrive(bar(L::kBarPReady + 2 * t + hb));
@@ -664,6 +707,13 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         auto issue_s = [&](int hb, int slot) {
           const uint32_t d_tmem = tSt + kHalfN * hb;
           if constexpr (QK8) {
+            // The accumulator starts at 1.5*2^23 in every element: one fp16 MMA of two constant
+            // tiles (3072 * 4096 in the k = 0 term, zeros elsewhere) writes the fp32 bit pattern
+            // 0x4B400000, and the int8 MMAs then add the integer dot products onto those bits.
+            // The softmax reads the words as the floats 12582912 + acc.
+            constexpr uint32_t idesc_bias = make_idesc(1, 0, 0, 0, kTileM, kHalfN);
+            mma_f16_ss(d_tmem, make_smem_desc(sbase + L::kOffBiasA, 16, 1024),
+                       make_smem_desc(sbase + L::kOffBiasB, 16, 1024), idesc_bias, 0u);
             // int8 rows are D bytes: 64-byte swizzle (8 rows = 512 B) at D=64, 128-byte at D=128;
             // one MMA consumes K = 32 bytes.
             constexpr uint32_t kLayout = (D == 64) ? 4u : 2u;
@@ -673,7 +723,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int k = 0; k < D / 32; ++k) {
               const uint64_t da = make_smem_desc(sQt + k * 32, 16, kSbo, kLayout);
               const uint64_t db = make_smem_desc(kb + k * 32, 16, kSbo, kLayout);
-              mma_i8_ss(d_tmem, da, db, idesc_s, k > 0);
+              mma_i8_ss(d_tmem, da, db, idesc_s, 1u);
             }
           } else {
             const uint32_t kb = sRing + slot * L::kTileBytes + hb * kHalfN * 128;
@@ -710,10 +760,23 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const uint32_t kpar = (cons / L::kStages) & 1;
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
+            // S_h(j+1).  With P in columns of its own (D = 64) it goes first, as soon as the softmax
+            // group holds S_h(j) in registers; otherwise after PV_h(j), whose operand P_h(j)
+            // lives in the S buffer.
+            auto next_s = [&]() {
+              if (!has_next) return;
+              if (hb == 0) mbar_wait(bar(L::kBarKvFull + kslot), kpar, wc, kErrWaitKV);
+              if constexpr (L::kSepP) mbar_wait(bar(L::kBarSFree + 2 * t + hb), j & 1, wc, kErrWaitP);
+              tc_fence_after();
+              issue_s(hb, kslot);
+              mma_commit(bar(L::kBarSFull + 2 * t + hb));
+              if (hb == 1) mma_commit(bar(L::kBarKvEmpty + kslot));
+            };
+            if constexpr (L::kSepP) next_s();
             mbar_wait(bar(L::kBarOReady + 2 * t + hb), j & 1, wc, kErrWaitCorr);
             mbar_wait(bar(L::kBarPReady + 2 * t + hb), j & 1, wc, kErrWaitP);
             tc_fence_after();
-            const uint32_t tP = tSt + kHalfN * hb;
+            const uint32_t tP = L::kSepP ? tmem_base + L::kColP + 64 * t + 32 * hb : tSt + kHalfN * hb;
 #pragma unroll
             for (int kk = 0; kk < kHalfN / 16; ++kk) {
               const int k = hb * (kHalfN / 16) + kk;  // 16-key slice of the V tile
@@ -723,15 +786,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             }
             mma_commit(bar(L::kBarODone + 2 * t + hb));
             if (hb == 1) mma_commit(bar(L::kBarKvEmpty + vslot));
-            if (has_next) {
-              if (hb == 0) {
-                mbar_wait(bar(L::kBarKvFull + kslot), kpar, wc, kErrWaitKV);
-                tc_fence_after();
-              }
-              issue_s(hb, kslot);
-              mma_commit(bar(L::kBarSFull + 2 * t + hb));
-              if (hb == 1) mma_commit(bar(L::kBarKvEmpty + kslot));
-            }
+            if constexpr (!L::kSepP) next_s();
           }
           if (has_next) ++cons;
         }
@@ -769,7 +824,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 // ---------------------------------------------------------------------------------
 template <int D, bool BF16, bool QK8, bool CARRY = false>
 static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_count, cudaStream_t st) {
-  using L = WsLayout<D>;
+  using L = WsLayout<D, QK8>;
   auto kern = fwd_ws_kernel<D, BF16, QK8, false, CARRY>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
@@ -801,7 +856,7 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_c
 template <int D, bool BF16, bool QK8>
 static cudaError_t launch_plan_t(const CUtensorMap* tm, const FwdArgs& a, const FwdPlan& plan,
                                  cudaStream_t st) {
-  using L = WsLayout<D>;
+  using L = WsLayout<D, QK8>;
   auto kern = fwd_ws_kernel<D, BF16, QK8, true>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);

@@ -300,6 +300,44 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// Packed fp32 pairs (one issue slot for two lanes of FMA / ADD on sm_100): a pair lives in a
+// 64-bit register, low word first.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// 2^x for a pair on the FMA pipe instead of the exp2 unit: x = n + f with n = round(x) taken from
+// the low mantissa bits of x + 1.5*2^23 and f in [-0.5, 0.5]; 2^f by a cubic (max relative error
+// 1.0e-4, below the half-ulp of a 16-bit P), n added into the exponent field.  Inputs below -126
+// (masked scores are -inf) give 2^-126, which rounds to 0 in 16 bit.
+__device__ __forceinline__ void exp2_poly_f32x2(float x0, float x1, float& p0, float& p1) {
+  const uint64_t x = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t xr = add_f32x2(x, pack_f32x2(12582912.f, 12582912.f));
+  const uint64_t n = add_f32x2(xr, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = fma_f32x2(n, pack_f32x2(-1.f, -1.f), x);
+  uint64_t p = fma_f32x2(f, pack_f32x2(0.05592204f, 0.05592204f), pack_f32x2(0.24264008f, 0.24264008f));
+  p = fma_f32x2(p, f, pack_f32x2(0.69312103f, 0.69312103f));
+  p = fma_f32x2(p, f, pack_f32x2(0.99992448f, 0.99992448f));
+  float r0, r1, q0, q1;
+  unpack_f32x2(xr, r0, r1);
+  unpack_f32x2(p, q0, q1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (BF16) {

@@ -6,7 +6,10 @@
 //      tokens: scale = max|x| / 127 over the 128 x D slab (1 for an all-zero slab),
 //      x8 = round-half-even(x / scale), clamped to [-127, 127].
 // Two launches: stage 1 quantises Q and sums the columns of K (independent work, one grid), stage 2
-// smooths and quantises K.  HBM-bound byte movers: 16-byte loads, 8-byte int8 stores, one CTA per
+// smooths and quantises K.  Stage 2 is launched as a programmatic dependent of stage 1: its CTAs
+// become resident while stage 1 drains and load their K slabs before they wait for stage 1's
+// column sums, so the second launch's ramp and first loads hide under the first one's tail.
+// HBM-bound byte movers: 16-byte loads, 8-byte int8 stores, one CTA per
 // (128-token block, head, batch) or per 1024-token column-sum chunk.  Algorithmic traffic per element: K 2 B (mean pass) + 2 B + 1 B,
 // Q 2 B + 1 B, plus 4 B per 128 x D slab for the scale.
 #include <cuda_bf16.h>
@@ -103,6 +106,8 @@ __device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long 
     if (row < N) raw[i] = *reinterpret_cast<const uint4*>(base + row * sn + col8 * 8);
   }
   if (SMOOTH) {
+    // everything above is independent of stage 1; its column sums are complete and visible from here
+    cudaGridDependencySynchronize();
     if (threadIdx.x < D) {
       float s = 0.f;
       const float* p = partial + (static_cast<long long>(b) * H + h) * n_chunks * D + threadIdx.x;
@@ -136,6 +141,7 @@ __device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long 
 #pragma unroll
   for (int w = 1; w < 8; ++w) amax = fmaxf(amax, wmax[w]);
   const float scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+  const float inv = __frcp_rn(scale);
   if (threadIdx.x == 0)
     scale_out[(static_cast<long long>(b) * H + h) * n_blocks + blk] = scale * fold;
   int8_t* obase = x8 + ((static_cast<long long>(b) * H + h) * N) * D;
@@ -150,8 +156,20 @@ __device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long 
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         if (SMOOTH) f[e] -= mean[col8 * 8 + e];
-        int qv = __float2int_rn(__fdiv_rn(f[e], scale));
-        qv = max(-127, min(127, qv));
+        // round-half-even(x / scale), bit for bit, without a division per element: y = x * (1/scale)
+        // is within 2e-5 of the true quotient, and adding 1.5*2^23 rounds it to the nearest integer
+        // (ties to even) in the low mantissa bits.  Only when y lies within 1e-3 of a tie can the
+        // two roundings differ; those elements (about 0.2 %) take the exact division.
+        const float y = f[e] * inv;
+        const float t = y + 12582912.f;
+        const float d = y - (t - 12582912.f);
+        int qv;
+        if (fabsf(d) > 0.499f) {
+          qv = __float2int_rn(__fdiv_rn(f[e], scale));
+          qv = max(-127, min(127, qv));
+        } else {
+          qv = __float_as_int(t) - 0x4B400000;
+        }
         if (e < 4) lo |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * e);
         else hi |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * (e - 4));
       }
@@ -168,6 +186,8 @@ prepass_stage1_kernel(const uint16_t* __restrict__ q, long long qsb, long long q
                       int Hq, int nqb, int8_t* __restrict__ q8, float* __restrict__ sq, float fold,
                       const uint16_t* __restrict__ k, long long ksb, long long ksh, long long ksn, int Nk,
                       int Hkv, int nch, float* __restrict__ partial, int q_blocks) {
+  // the dependent launch (stage 2) may start as soon as every CTA of this grid is under way
+  cudaTriggerProgrammaticLaunchCompletion();
   const int id = blockIdx.x;
   if (id < q_blocks) {
     const int blk = id % nqb, h = (id / nqb) % Hq, b = id / (nqb * Hq);
@@ -204,9 +224,20 @@ static cudaError_t launch_quant_t(const void* q, const long long* qs, const void
     prepass_stage1_kernel<D, BF16><<<static_cast<unsigned>(q_blocks + s_blocks), 256, 0, st>>>(
         static_cast<const uint16_t*>(q), qs[0], qs[1], qs[2], Nq, Hq, nqb, q8, sq, q_fold,
         static_cast<const uint16_t*>(k), ks[0], ks[1], ks[2], Nk, Hkv, nch, partial, static_cast<int>(q_blocks));
-  if (Nk > 0)
-    quant_k_kernel<D, BF16><<<dim3(nkb, Hkv, B), 256, 0, st>>>(static_cast<const uint16_t*>(k), ks[0], ks[1], ks[2],
-                                                             Nk, partial, nch, k8, sk, k_mean);
+  if (Nk > 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nkb, Hkv, B);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (q_blocks + s_blocks > 0) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, quant_k_kernel<D, BF16>, static_cast<const uint16_t*>(k), ks[0], ks[1],
+                                       ks[2], Nk, static_cast<const float*>(partial), nch, k8, sk, k_mean);
+    if (e != cudaSuccess) return e;
+  }
   return cudaGetLastError();
 }
 
