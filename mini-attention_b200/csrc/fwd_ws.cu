@@ -832,10 +832,10 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_c
   const long long n_pairs = (a.n_q_tiles + 1) / 2;
   const long long items = n_pairs * a.Hq * a.B;
   if (items > 0x7fffffffll) return cudaErrorInvalidValue;
-  // One CTA per SM: `items` CTAs run in ceil(items / SMs) waves.  When the last wave would be at
-  // most half full, its pairs are split into single-tile CTAs (twice as many, each shorter), which
-  // still fit one wave; needs every tile to be real (even tile count) and enough K/V tiles to
-  // amortise a CTA.
+  // One CTA per SM: `items` CTAs run in ceil(items / SMs) waves.  When the last (or only) wave
+  // would be at most half full, its pairs are split into single-tile CTAs (twice as many, each
+  // shorter), which still fit one wave; needs every tile to be real (even tile count) and enough
+  // K/V tiles to amortise a CTA (measured: a gain from 4 tiles on).
   FwdArgs args = a;
   args.n_pair_items = static_cast<int>(items);
   args.part_o = nullptr;
@@ -844,7 +844,7 @@ static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_c
   long long grid = items;
   const long long rest = sm_count > 0 ? items % sm_count : 0;
   const long long kv_tiles = (a.Nk + kTileN - 1) / kTileN;
-  if (items > sm_count && rest > 0 && 2 * rest <= sm_count && (a.n_q_tiles % 2) == 0 && kv_tiles >= 8) {
+  if (rest > 0 && 2 * rest <= sm_count && (a.n_q_tiles % 2) == 0 && (kv_tiles >= 8 || (items < sm_count && kv_tiles >= 4))) {
     args.n_pair_items = static_cast<int>(items - rest);
     grid = items + rest;
   }

@@ -227,6 +227,21 @@ def ring_forward(
     return out
 
 
+def ring_process_group(ranks: Optional[Sequence[int]] = None):
+    """A process group for :func:`ring_forward` whose NCCL stream has high priority.
+
+    The attention kernel fills every SM with one CTA and keeps hundreds more queued, so the CTAs of
+    a send/recv kernel on an ordinary stream are dispatched only as attention CTAs retire and the
+    transfer starts late; on a high-priority stream they are dispatched first.  Measured on 8 GPUs
+    (config 5, 268 MB per hop): 20.9 ms per ring pass with the default group, 20.0 ms with this one,
+    18.3 ms for the same launches without any transfer.  Creating a group initialises a new NCCL
+    communicator (seconds): make it once and pass it as ``group=``.  Collective over `ranks`
+    (default: all)."""
+    import torch.distributed as dist
+    opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+    return dist.new_group(list(ranks) if ranks is not None else None, pg_options=opts)
+
+
 class _P2PHandle:
     def __init__(self, works, tag_recv):
         self.works = works

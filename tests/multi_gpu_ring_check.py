@@ -34,6 +34,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ok = True
+    hp_group = par.ring_process_group()   # the launcher's high-priority group; the default group is used too
     for dtype, tol in ((torch.float16, 2e-3), (torch.bfloat16, 1e-2)):
         g = torch.Generator().manual_seed(7)
         N, H, D = args.seq_len, 4, 128
@@ -45,7 +46,7 @@ def main():
         out = par.ring_forward(qs, ks, vs, causal=True, rank=rank, world=world, verify_origin=True)
         err = (out.float() - par.zigzag_split(full, world)[rank].float()).abs().max().item()
         # the two-launch form (16-bit partials + merge kernel) over the same ring
-        out2 = par.ring_forward(qs, ks, vs, causal=True, rank=rank, world=world, fused=False)
+        out2 = par.ring_forward(qs, ks, vs, causal=True, rank=rank, world=world, fused=False, group=hp_group)
         err = max(err, (out2.float() - par.zigzag_split(full, world)[rank].float()).abs().max().item())
         line = f"rank {rank}/{world} ring {dtype}: max|ring - single| = {err:.3e}"
         if rank == 0:

@@ -318,6 +318,23 @@ def test_last_wave_single_tile_ctas():
         assert maxerr(out, simple) <= TOL[torch.float16]
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_one_wave_single_tile_ctas(causal):
+    """32 tile pairs for 148 SMs (config 2 at N = 512): a launch of less than half a wave runs every
+    pair as two single-tile CTAs; with a carried state the second tile's CTA finds its own rows."""
+    q, k, v = make_inputs(2, 8, 8, 512, 512, 128, torch.float16, seed=12)
+    ref = attention_reference(q, k, v, causal=causal, out_dtype=torch.float32)
+    out = run(q, k, v, causal=causal, kernel="ws")
+    assert maxerr(out, ref) <= TOL[torch.float16]
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    state = miniattn.carry_state(qd)
+    miniattn.flash_attn_fwd(qd, kd[:, :, :256], vd[:, :, :256], causal=causal, carry=state, carry_out=True)
+    out2 = miniattn.flash_attn_fwd(qd, kd[:, :, 256:], vd[:, :, 256:], causal=causal, k_pos0=256, carry=state,
+                                   carry_in=True)
+    assert miniattn.device_status(DEV) == 0
+    assert maxerr(out2.cpu(), ref) <= TOL[torch.float16]
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("causal", [False, True])
