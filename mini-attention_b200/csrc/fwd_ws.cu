@@ -71,19 +71,13 @@ struct WsLayout {
   static constexpr int kBarOReady = kBarAlpha + 4;         // [2][2] correction -> MMA
   static constexpr int kBarODone = kBarOReady + 4;         // [2][2] MMA -> correction
   static constexpr int kBarStagger = kBarODone + 4;        // one-shot: tile 0 published its first row maxima
-  static constexpr int kBarSFree = kBarStagger + 1;        // [2][2] softmax -> MMA: S half is in registers (D = 64)
-  static constexpr int kNumBars = kBarSFree + 4;
+  static constexpr int kNumBars = kBarStagger + 1;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem slot, abort flag, arrival order [2]
   static constexpr int kBytes = kOffMisc + 32;
   static constexpr int kDynSmem = kBytes + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0;     // S buffer of (tile t, half h) at kColS + 128*t + 64*h
   static constexpr int kColO = 256;   // O accumulator of tile t at kColO + D*t
-  // At D = 64 the two O accumulators leave 128 columns free: P gets a region of its own
-  // (tile t, half h at kColP + 64*t + 32*h) instead of overwriting its S buffer, so S_h(j+1) can
-  // be issued as soon as the softmax group holds S_h(j) in registers.
-  static constexpr bool kSepP = false;
-  static constexpr int kColP = 384;
 };
 
 constexpr int kBarEpilogue = 1;  // named barriers 1 and 2: epilogue of softmax group 0 / 1
@@ -230,7 +224,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (i >= L::kBarKvEmpty && i < L::kBarSFull) count = nt;      // one release per issuing thread
       else if (i >= L::kBarPReady && i < L::kBarODone) count = 4;   // P ready, alpha, O ready: 4 warps
       else if (i == L::kBarStagger) count = 4;                      // the 4 softmax warps of tile 0, once
-      else if (i >= L::kBarSFree) count = 4;                        // S in registers: 4 warps
       mbar_init(bar(i), count);
     }
     if (lane == 0) *abort_flag = 0;
@@ -308,10 +301,6 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tmem_ld32(tS + hb * kHalfN, s[0]);
           tmem_ld32(tS + hb * kHalfN + 32, s[1]);
           tmem_wait_ld();
-          if constexpr (L::kSepP) {  // the scores are in registers: the MMA role may refill this half
-            tc_fence_before();
-            warp_arrive(bar(L::kBarSFree + 2 * t + hb));
-          }
           // QK8: the accumulator was started at the bit pattern of 1.5*2^23 (see issue_s) and
           // |acc| <= 127*127*D < 2^22, so the word read here IS the float 12582912 + acc: int32 ->
           // fp32 with no instruction at all.  The offset stays in: it is order-preserving for the
@@ -357,9 +346,11 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           float mc = (m_cur == -INFINITY) ? 0.f : m_cur;
           if constexpr (QK8) mc = fmaf(kBias, cj, mc);
           // two scores per FMA / ADD issue slot (packed f32x2); the exp2 itself is one per lane,
-          // except that one pair in eight is evaluated by a polynomial on the FMA pipe: the exp2
-          // unit (16 results per clock per SM) is co-critical with the tensor pipe, the FMA pipe
-          // has room (larger shares measured slower: the issue slots run out)
+          // except that one pair in eight (one in four at D = 64, where the exp2 unit is the
+          // bound) is evaluated by a polynomial on the FMA pipe: the exp2 unit (16 results per
+          // clock per SM) is co-critical with the tensor pipe, the FMA pipe has room.  Larger
+          // shares measured slower (3/8 and 1/2: the issue slots run out).
+          constexpr int kPolyMask = (D == 64) ? 7 : 15;
           uint64_t psum = pack_f32x2(0.f, 0.f);
           const uint64_t cj2 = pack_f32x2(cj, cj), mc2 = pack_f32x2(-mc, -mc);
           uint32_t pk[32];
@@ -371,7 +362,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[q][i]), __uint_as_float(s[q][i + 1])), cj2, mc2),
                            x0, x1);
               float p0, p1;
-              if ((i & 15) == 0) {
+              if ((i & kPolyMask) == 0) {
                 exp2_poly_f32x2(x0, x1, p0, p1);
               } else {
                 p0 = ex2(x0);
@@ -383,14 +374,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           float psum0, psum1;
           unpack_f32x2(psum, psum0, psum1);
           l_run = l_run * alpha + (psum0 + psum1);
-          if constexpr (L::kSepP) {
-            // P has its own columns; the PV MMA of the previous step must be done reading them
-            if (j > 0) mbar_wait(bar(L::kBarODone + 2 * t + hb), (j - 1) & 1, wc, kErrWaitO);
-            tc_fence_after();
-            tmem_st32(tmem_base + L::kColP + 64 * t + 32 * hb + lane_off, pk);
-          } else {
-            tmem_st32(tS + hb * kHalfN, pk);  // P of this half over the first 32 columns of its S
-          }
+          tmem_st32(tS + hb * kHalfN, pk);  // P of this half over the first 32 columns of its S
           tmem_wait_st();
           tc_fence_before();
           warp_arrive(bar(L::kBarPReady + 2 * t + hb));
@@ -760,23 +744,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const uint32_t kpar = (cons / L::kStages) & 1;
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
-            // S_h(j+1).  With P in columns of its own (D = 64) it goes first, as soon as the softmax
-            // group holds S_h(j) in registers; otherwise after PV_h(j), whose operand P_h(j)
-            // lives in the S buffer.
-            auto next_s = [&]() {
-              if (!has_next) return;
-              if (hb == 0) mbar_wait(bar(L::kBarKvFull + kslot), kpar, wc, kErrWaitKV);
-              if constexpr (L::kSepP) mbar_wait(bar(L::kBarSFree + 2 * t + hb), j & 1, wc, kErrWaitP);
-              tc_fence_after();
-              issue_s(hb, kslot);
-              mma_commit(bar(L::kBarSFull + 2 * t + hb));
-              if (hb == 1) mma_commit(bar(L::kBarKvEmpty + kslot));
-            };
-            if constexpr (L::kSepP) next_s();
             mbar_wait(bar(L::kBarOReady + 2 * t + hb), j & 1, wc, kErrWaitCorr);
             mbar_wait(bar(L::kBarPReady + 2 * t + hb), j & 1, wc, kErrWaitP);
             tc_fence_after();
-            const uint32_t tP = L::kSepP ? tmem_base + L::kColP + 64 * t + 32 * hb : tSt + kHalfN * hb;
+            const uint32_t tP = tSt + kHalfN * hb;
 #pragma unroll
             for (int kk = 0; kk < kHalfN / 16; ++kk) {
               const int k = hb * (kHalfN / 16) + kk;  // 16-key slice of the V tile
@@ -786,7 +757,15 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             }
             mma_commit(bar(L::kBarODone + 2 * t + hb));
             if (hb == 1) mma_commit(bar(L::kBarKvEmpty + vslot));
-            if constexpr (!L::kSepP) next_s();
+            if (has_next) {  // S_h(j+1) after PV_h(j), whose operand P_h(j) lives in the S buffer
+              if (hb == 0) {
+                mbar_wait(bar(L::kBarKvFull + kslot), kpar, wc, kErrWaitKV);
+                tc_fence_after();
+              }
+              issue_s(hb, kslot);
+              mma_commit(bar(L::kBarSFull + 2 * t + hb));
+              if (hb == 1) mma_commit(bar(L::kBarKvEmpty + kslot));
+            }
           }
           if (has_next) ++cons;
         }
