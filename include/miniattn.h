@@ -141,10 +141,13 @@ typedef struct MiniAttnPlanInfo {
   int64_t scratch_bytes;
   float est_plain;       /* predicted makespans in K/V-tile steps (128 keys) of one CTA         */
   float est_balanced;
+  int32_t head_group;    /* items walk the (batch, head) indices in groups of this many; B*Hq = all at once */
 } MiniAttnPlanInfo;
 
 typedef struct MiniAttnPlanPiece {
-  int32_t item;          /* index in launch order: Q-tile pair n_pairs-1 - item/(B*Hq), heads fastest */
+  int32_t item;          /* index in launch order.  With G = head_group and P Q-tile pairs per head:  */
+                         /* group item/(P*G) of G consecutive (batch, head) indices; inside it pair   */
+                         /* P-1 - (item%(P*G))/G (latest rows first) and head (item%(P*G))%G          */
   int32_t t0, t1;        /* K/V tiles [t0, t1) of the item                                      */
   int32_t part, nparts;  /* nparts == 1: the whole item                                         */
   int32_t slot;          /* partial slot of a piece of a cut item, -1 otherwise                 */

@@ -18,6 +18,9 @@ struct FwdArgs {
   int n_q_tiles;       // ceil(Nq / 128)
   int n_pair_items;    // warp-specialised kernel: CTAs [0, n_pair_items) take two Q tiles each,
                        // the CTAs after them one Q tile each (the tail of the last wave)
+  int bh_group;        // work items are ordered in groups of this many consecutive (batch, head)
+                       // indices: all Q-tile pairs of a group (latest first, heads fastest) before the
+                       // next group.  B*Hq = one group, the default order.  Divides B*Hq.
   const float* sq;     // INT8-QK: [B, Hq,  ceil(Nq/128)] Q scales (softmax scale * log2e folded in)
   const float* sk;     // INT8-QK: [B, Hkv, ceil(Nk/128)] K scales
   // Balanced launches only (null otherwise): where CTAs that cover part of an item's key range
@@ -59,6 +62,17 @@ constexpr int kTileM = 128;   // query rows per MMA tile (TMEM lanes)
 constexpr int kTileN = 128;   // keys per K/V tile
 constexpr int kBoxCols = 64;  // 16-bit elements per 128-byte swizzled row
 constexpr int kBoxBytes = kTileN * 128;  // one [128 rows x 128 B] TMA box
+
+// Work item -> (Q-tile pair, (batch, head) index).  Items walk the (batch, head) indices in groups
+// of a.bh_group: within a group the latest Q-tile pair first (the heaviest under a causal mask) and
+// heads fastest, so that the CTAs in flight share the K/V of few heads.  Shared by the kernels and
+// the host planner.
+__host__ __device__ inline void item_to_pair_bh(const FwdArgs& a, int n_pairs, int item, int* pair, int* bh) {
+  const int per_group = n_pairs * a.bh_group;
+  const int within = item % per_group;
+  *pair = n_pairs - 1 - within / a.bh_group;
+  *bh = (item / per_group) * a.bh_group + within % a.bh_group;
+}
 
 // Number of K/V tiles the Q rows [q0, q0 + nt*128) have to visit (all of them without a mask,
 // up to the diagonal of the last row with one).  Shared by the kernels and the host planner.

@@ -162,8 +162,8 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       single = s_idx & 1;
     }
   }
-  const int pair = n_pairs - 1 - item / bh_total;
-  const int bh = item % bh_total;
+  int pair, bh;
+  item_to_pair_bh(a, n_pairs, item, &pair, &bh);
   const int h = bh % a.Hq;
   const int b = bh / a.Hq;
   const int hk = h / (a.Hq / a.Hkv);

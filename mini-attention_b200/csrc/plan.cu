@@ -18,7 +18,6 @@
 // longest first.  The plan is used only when its predicted makespan beats the plain launch.
 #include <algorithm>
 #include <cmath>
-#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <queue>
@@ -68,23 +67,10 @@ constexpr int kMaxParts = 64;      // pieces per item
 
 // Cost model, in steps (one K/V tile of a two-Q-tile CTA, about 2 us at D = 128): fixed cost of
 // a CTA, and what a piece of a cut item adds on average (publishing its partial takes about 0.6
-// steps; the last piece to arrive also reads the others', about 2 steps).  MINIATTN_PLAN_CTA_COST / MINIATTN_PLAN_PIECE_COST override them for measurements.
-float env_or(const char* name, float dflt) {
-  const char* v = getenv(name);
-  return (v != nullptr && *v != 0) ? static_cast<float>(atof(v)) : dflt;
-}
-float cta_cost(int D) {
-  static const float v = env_or("MINIATTN_PLAN_CTA_COST", -1.f);
-  return v >= 0.f ? v : (D == 128 ? 2.0f : 3.0f);
-}
-float grade_frac() {  // MINIATTN_PLAN_GRADE: spread of the per-SM targets, as a fraction of T
-  static const float v = env_or("MINIATTN_PLAN_GRADE", 0.015f);
-  return v;
-}
-float piece_cost() {
-  static const float v = env_or("MINIATTN_PLAN_PIECE_COST", 1.3f);
-  return v;
-}
+// steps; the last piece to arrive also reads the others', about 2 steps).
+float cta_cost(int D) { return D == 128 ? 2.0f : 3.0f; }
+float grade_frac() { return 0.015f; }  // spread of the per-SM targets, as a fraction of T
+float piece_cost() { return 1.3f; }
 
 // Fill under the target time T.  Phase 1: items go whole to the least-loaded SM while they fit.
 // Phase 2, from the first item that does not: the SMs are filled one after the other up to T
@@ -162,7 +148,7 @@ bool fill(const std::vector<int>& w, int sms, float T, float h, float fee, std::
 
 }  // namespace
 
-// Items in launch order: item i covers the Q-tile pair n_pairs-1 - i / (B*Hq) (latest rows first).
+// Items in launch order (item_to_pair_bh): latest rows first within each group of heads.
 void plan_fwd(const FwdArgs& a, int D, int sms, FwdPlan* plan) {
   plan->split = false;
   plan->n_whole = plan->n_table = plan->n_slots = plan->n_cut_items = 0;
@@ -179,7 +165,8 @@ void plan_fwd(const FwdArgs& a, int D, int sms, FwdPlan* plan) {
   std::vector<int> w(n);
   long long total = 0;
   for (int i = 0; i < n; ++i) {
-    const int pair = static_cast<int>(n_pairs - 1 - i / bh);
+    int pair, bh_i;
+    item_to_pair_bh(a, static_cast<int>(n_pairs), i, &pair, &bh_i);
     const int q0 = pair * 2 * kTileM;
     const int nt = (q0 + kTileM < a.Nq) ? 2 : 1;
     w[i] = kv_tiles_of(a, q0, nt);

@@ -60,6 +60,7 @@ class PlanInfo(C.Structure):
         ("split", C.c_int32), ("sm_count", C.c_int32), ("n_ctas", C.c_int64),
         ("n_whole", C.c_int32), ("n_pieces", C.c_int32), ("n_cut_items", C.c_int32), ("n_slots", C.c_int32),
         ("scratch_bytes", C.c_int64), ("est_plain", C.c_float), ("est_balanced", C.c_float),
+        ("head_group", C.c_int32),
     ]
 
 

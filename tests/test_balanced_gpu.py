@@ -110,3 +110,25 @@ def test_repeated_balanced_launches_stay_one_rounding_from_the_plain_launch():
     torch.cuda.synchronize()
     assert miniattn.device_status(DEV) == 0
     assert worst <= 5e-4 and worst_lse <= 1e-5
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_head_groups_when_k_and_v_outgrow_l2(causal):
+    """8 heads x 16384 keys x D=128: 67 MB of K and V, so the work items walk the heads in groups
+    (a share of L2 each) instead of all at once.  Plain and balanced launches against the kernel
+    that has its own, fixed order and against the exact oracle on sampled rows."""
+    from oracle.attention_oracle import attention_reference_rows
+    B, H, N, D = 1, 8, 16384, 128
+    info, _ = plan_info(B, H, N, N, D, causal=causal, sm_count=sms())
+    assert 0 < info.head_group < B * H and (B * H) % info.head_group == 0
+    q, k, v = make_inputs(B, H, H, N, N, D, torch.float16, seed=3)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    simple = miniattn.flash_attn_fwd(qd, kd, vd, causal=causal, kernel="simple")
+    plain = miniattn.flash_attn_fwd(qd, kd, vd, causal=causal, balance=False)
+    bal = miniattn.flash_attn_fwd(qd, kd, vd, causal=causal, balance=True)
+    assert miniattn.device_status(DEV) == 0
+    assert (plain.float() - simple.float()).abs().max().item() <= TOL[torch.float16]
+    assert (bal.float() - plain.float()).abs().max().item() <= 5e-4
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, N // 2 - 1, N // 2, N - 257, N - 256, N - 129, N - 1])
+    ref = attention_reference_rows(q, k, v, rows, causal=causal)
+    assert (bal[:, :, rows.to(DEV)].float().cpu() - ref).abs().max().item() <= TOL[torch.float16]

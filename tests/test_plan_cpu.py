@@ -13,10 +13,12 @@ from miniattn.ops import plan_info
 SMS = 148
 
 
-def item_tiles(item, B, Hq, Nq, Nk, causal, q_pos0=0, k_pos0=0):
-    """K/V tiles of work item `item` (pair of 128-row Q tiles; latest rows first, heads fastest)."""
+def item_tiles(item, B, Hq, Nq, Nk, causal, q_pos0=0, k_pos0=0, group=None):
+    """K/V tiles of work item `item` (pair of 128-row Q tiles): heads walked in groups of `group`
+    (all B*Hq at once by default), inside a group latest rows first, heads fastest."""
     n_pairs = ((Nq + 127) // 128 + 1) // 2
-    pair = n_pairs - 1 - item // (B * Hq)
+    group = group or B * Hq
+    pair = n_pairs - 1 - (item % (n_pairs * group)) // group
     q0 = pair * 256
     nt = 2 if q0 + 128 < Nq else 1
     kv_end = Nk
@@ -58,7 +60,7 @@ def test_pieces_tile_every_item_once(case):
     cut = 0
     for item, lst in by_item.items():
         lst.sort()
-        w = item_tiles(item, B, Hq, Nq, Nk, causal, qp, kp)
+        w = item_tiles(item, B, Hq, Nq, Nk, causal, qp, kp, info.head_group)
         assert [x[0] for x in lst] == list(range(len(lst)))
         assert all(x[3] == len(lst) for x in lst)
         assert lst[0][1] == 0 and lst[-1][2] == w, (item, lst, w)
@@ -130,7 +132,7 @@ def test_random_shapes_keep_the_invariants():
         assert len(cover) == n_items - info.n_whole
         for item, lst in cover.items():
             lst.sort()
-            w = item_tiles(item, B, Hq, Nq, Nk, causal, qp, kp)
+            w = item_tiles(item, B, Hq, Nq, Nk, causal, qp, kp, info.head_group)
             assert lst[0][0] == 0 and lst[-1][1] == w and all(a[1] == b_[0] for a, b_ in zip(lst, lst[1:]))
             assert all(x[2] == len(lst) for x in lst)
             assert all((x[3] >= 0) == (len(lst) > 1) for x in lst)
