@@ -526,7 +526,6 @@ def main():
         value = total_flops / ms_dev / 1e9
         achieved = step_flops / ms_dev / 1e9
         cfg = workload_config(w, world)
-        cfg["per_gpu"] = shard
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_dev, "ms_per_step_median_rank0": ms_dev_median,
@@ -534,7 +533,8 @@ def main():
             "vs_baseline": None, "dtype": ("int8 QK^T (s32 acc) + " + w["dtype"] + " PV" if w.get("int8qk") else w["dtype"]),
             "data": "synthetic",
             "config": cfg,
-            "method": {"parallelism": (f"zig-zag ring over {world} GPU(s): NCCL send/recv of K/V pairs, running state "
+            "method": {"per_gpu": shard,
+                       "parallelism": (f"zig-zag ring over {world} GPU(s): NCCL send/recv of K/V pairs, running state "
                                        "carried inside the attention kernel" if ring
                                        else f"batch x head shards over {world} GPU(s), no communication"),
                        "launch": "plain" if args.no_balance else "balanced (key ranges cut to fill the last round of CTAs)",
