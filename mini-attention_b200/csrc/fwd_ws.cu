@@ -28,6 +28,7 @@
 // The row maximum is updated lazily: a row keeps exponentiating against a stale maximum until the
 // true maximum has grown by more than 2^8 (in the exp2 domain), so the O accumulator is rescaled
 // only rarely; l is accumulated against the same maximum, which keeps O / l exact.
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -801,12 +802,27 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 }
 
 // ---------------------------------------------------------------------------------
+// The opt-in to more than 48 KB of dynamic shared memory is per function and per device; it is
+// made once for each (the reference does it at import, flash_attention.cu:140-147), not on every
+// launch.  `done` holds one bit per device ordinal.
+template <typename Kernel>
+static cudaError_t allow_dynamic_smem(Kernel kern, int bytes, std::atomic<unsigned long long>* done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && ((done->load(std::memory_order_acquire) >> dev) & 1ull)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && tracked) done->fetch_or(1ull << dev, std::memory_order_release);
+  return e;
+}
+
 template <int D, bool BF16, bool QK8, bool CARRY = false>
 static cudaError_t launch_ws_t(const CUtensorMap* tm, const FwdArgs& a, int sm_count, cudaStream_t st) {
   using L = WsLayout<D, QK8>;
   auto kern = fwd_ws_kernel<D, BF16, QK8, false, CARRY>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
+  static std::atomic<unsigned long long> smem_set{0};  // per instantiation: devices already configured
+  cudaError_t e = allow_dynamic_smem(kern, L::kDynSmem, &smem_set);
   if (e != cudaSuccess) return e;
   const long long n_pairs = (a.n_q_tiles + 1) / 2;
   const long long items = n_pairs * a.Hq * a.B;
@@ -837,8 +853,8 @@ static cudaError_t launch_plan_t(const CUtensorMap* tm, const FwdArgs& a, const 
                                  cudaStream_t st) {
   using L = WsLayout<D, QK8>;
   auto kern = fwd_ws_kernel<D, BF16, QK8, true>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
+  static std::atomic<unsigned long long> smem_set{0};
+  cudaError_t e = allow_dynamic_smem(kern, L::kDynSmem, &smem_set);
   if (e != cudaSuccess) return e;
   FwdArgs args = a;
   args.n_pair_items = plan.n_whole;

@@ -19,6 +19,11 @@ from . import _lib
 _DTYPES = {torch.float16: _lib.FP16, torch.bfloat16: _lib.BF16}
 _status_words: dict = {}
 _balance_scratch: dict = {}   # (device index, stream) -> zero-initialised uint8 scratch tensor
+# Parameter blocks of recent calls, keyed by everything that goes into one (pointers, shapes, strides,
+# dtype, flags).  A training or serving loop calls the operator with the same tensors again and again;
+# validating and filling the block costs more host time than a short-sequence kernel runs for.
+_param_cache: dict = {}
+_PARAM_CACHE_MAX = 256
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -199,31 +204,77 @@ def flash_attn_fwd(
     use_carry = bool(carry_in or carry_out)
     if use_carry and carry is None:
         raise RuntimeError("carry_in / carry_out need a carry buffer (carry_state)")
-    p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0,
-                           need_out=not carry_out)
-    if p is not None and use_carry:
-        need_c = _lib.lib.miniattn_fwd_carry_bytes(C.byref(p))
-        if need_c < 0:
-            _lib.check(int(need_c), "miniattn_fwd_carry_bytes")
-        if not carry.is_cuda or carry.device != q.device or carry.numel() * carry.element_size() < need_c:
-            raise RuntimeError(f"carry must be a CUDA buffer on q's device of at least {need_c} bytes")
-        p.carry, p.carry_in, p.carry_out = carry.data_ptr(), int(bool(carry_in)), int(bool(carry_out))
-    if p is not None:
-        with torch.cuda.device(q.device):
-            stream = torch.cuda.current_stream(q.device).cuda_stream
-            need = _lib.lib.miniattn_fwd_balanced_scratch_bytes(C.byref(p)) if balance and not use_carry else 0
+    # Fast path: the same tensors and flags as an earlier call.  Only a caller-provided `out` can be
+    # part of the key; a fresh output (and lse) is allocated per call and patched into the block.
+    try:
+        key = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr() if out is not None else 0,
+               q.shape, q.stride(), k.shape, k.stride(), v.stride(), out.stride() if out is not None else None,
+               q.dtype, q.device.index, causal, softmax_scale, layout, return_lse, kernel, q_pos0, k_pos0, balance,
+               carry.data_ptr() if carry is not None else 0, carry_in, carry_out)
+        hit = _param_cache.get(key)
+    except (AttributeError, TypeError):   # not tensors: let the validation below say so
+        key, hit = None, None
+    if hit is not None:
+        p, need = hit
+        lse = None
+        if not carry_out and (out is None or return_lse):
+            p = _lib.FwdParams.from_buffer_copy(p)   # the cached block stays as it is (other threads may hold it)
+            if out is None:
+                out = torch.empty_like(q)
+                p.o = out.data_ptr()
+            if return_lse:
+                lse = torch.empty((p.B, p.Hq, p.Nq), dtype=torch.float32, device=q.device)
+                p.lse = lse.data_ptr()
+    else:
+        out_given = out is not None
+        p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0,
+                               need_out=not carry_out)
+        if p is not None and use_carry:
+            need_c = _lib.lib.miniattn_fwd_carry_bytes(C.byref(p))
+            if need_c < 0:
+                _lib.check(int(need_c), "miniattn_fwd_carry_bytes")
+            if not carry.is_cuda or carry.device != q.device or carry.numel() * carry.element_size() < need_c:
+                raise RuntimeError(f"carry must be a CUDA buffer on q's device of at least {need_c} bytes")
+            p.carry, p.carry_in, p.carry_out = carry.data_ptr(), int(bool(carry_in)), int(bool(carry_out))
+        need = 0
+        if p is not None and balance and not use_carry:
+            with torch.cuda.device(q.device):
+                need = int(_lib.lib.miniattn_fwd_balanced_scratch_bytes(C.byref(p)))
             if need < 0:
-                _lib.check(int(need), "miniattn_fwd_balanced_scratch_bytes")
-            if need > 0:
-                scratch = _scratch_for(q.device, stream, int(need))
-                rc = _lib.lib.miniattn_fwd_balanced(C.byref(p), C.c_void_p(scratch.data_ptr()),
-                                                    C.c_size_t(scratch.numel()), C.c_void_p(stream))
-            else:
-                rc = _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
+                _lib.check(need, "miniattn_fwd_balanced_scratch_bytes")
+        # a freshly allocated output keeps the same strides from call to call (torch.empty_like)
+        if p is not None and key is not None and (out_given or out is None or out.stride() == q.stride()):
+            if len(_param_cache) >= _PARAM_CACHE_MAX:
+                _param_cache.clear()
+            _param_cache[key] = (p, need)
+    if p is not None:
+        dev_index = q.device.index
+        if torch.cuda.current_device() == dev_index:
+            rc = _launch_fwd(p, need, q.device, _current_raw_stream(dev_index))
+        else:
+            with torch.cuda.device(q.device):
+                rc = _launch_fwd(p, need, q.device, _current_raw_stream(dev_index))
         _lib.check(rc, "miniattn_fwd")
     if carry_out:
         return None
     return (out, lse) if return_lse else out
+
+
+def _current_raw_stream(device_index: int) -> int:
+    """cudaStream_t of torch's current stream on the device, without building a Stream object (3 us
+    of the 13 us a short-sequence call spends on the host)."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(device_index)
+    except AttributeError:
+        return torch.cuda.current_stream(device_index).cuda_stream
+
+
+def _launch_fwd(p, need: int, device: torch.device, stream: int) -> int:
+    if need > 0:
+        scratch = _scratch_for(device, stream, need)
+        return _lib.lib.miniattn_fwd_balanced(C.byref(p), C.c_void_p(scratch.data_ptr()),
+                                              C.c_size_t(scratch.numel()), C.c_void_p(stream))
+    return _lib.lib.miniattn_fwd(C.byref(p), C.c_void_p(stream))
 
 
 def carry_state(q: torch.Tensor, layout: str = "bhnd") -> torch.Tensor:
