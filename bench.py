@@ -366,6 +366,21 @@ def main():
         tot = flops(B, Hq, N, D, causal)
         return dict(B=B, Hq=Hq, Hkv=Hkv, N=N), "weak", tot * world, tot
 
+    def ring_parity_check(grp):
+        """The same ring (same transport, same kernels) on a sequence short enough for one launch:
+        every rank's rows against the single-launch kernel over the whole sequence, untimed."""
+        n_chk = 4096 * world
+        gen = torch.Generator(device=dev).manual_seed(99)   # same tensors on every rank
+        full = [torch.randn(1, 8, n_chk, 128, device=dev, dtype=torch.float16, generator=gen) for _ in range(3)]
+        single = miniattn.flash_attn_fwd(*full, causal=True)
+        mine = [par.zigzag_split(t_, world)[rank].contiguous() for t_ in full]
+        out = par.ring_forward(*mine, causal=True, rank=rank, world=world, group=grp, verify_origin=world > 1)
+        err = (out.float() - par.zigzag_split(single, world)[rank].float()).abs().max()
+        if world > 1:
+            dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        return {"what": f"ring over {world} rank(s) vs one launch, causal fp16 B=1 H=8 N={n_chk} D=128, origin tags verified",
+                "max_abs_diff": float(err.item()), "tolerance": 2e-3, "ok": bool(err.item() <= 2e-3)}
+
     def device_leg(key, steps, warmup):
         """Device-timed run of another workload on the same ranks (inputs made on the device)."""
         wl = WORKLOADS[key]
@@ -390,6 +405,7 @@ def main():
             grp = get_ring_group()
             ms = timed(lambda: par.ring_forward(ql, kl, vl, causal=True, rank=rank, world=world, group=grp), steps, warmup)
             res["launches_per_step"] = sum(len(par.ring_step_tasks(rank, world, s_, True)) for s_ in range(world))
+            res["parity_check"] = ring_parity_check(grp)
         else:
             ol = torch.empty_like(ql)
             ms = timed(lambda: miniattn.flash_attn_fwd(ql, kl, vl, causal=wl["causal"], out=ol), steps, warmup)

@@ -69,7 +69,9 @@ extern "C" {
  * carry_out = 1; middle calls: both 1; last call: carry_in = 1, carry_out = 0 —
  * only that one writes o (and lse).  While carry_out = 1 nothing is written to
  * o, which may then be NULL.  Nothing is rounded to 16 bit between the calls.
- * Calls with carried state always take the plain launch.
+ * Calls with carried state always take the plain launch.  A state sized for a
+ * longer q (miniattn_fwd_carry_bytes of that q) also serves calls on a row
+ * range of it that starts on a multiple of 128 rows: carry_tile0, carry_tiles.
  */
 typedef struct MiniAttnFwdParams {
   const void* q;          /* [B, Hq,  Nq, D] logical, device memory                */
@@ -93,6 +95,11 @@ typedef struct MiniAttnFwdParams {
   void*   carry;          /* running state of the rows between ring steps, or NULL */
   int32_t carry_in;       /* 1: fold the state in `carry` into this call's result  */
   int32_t carry_out;      /* 1: store the new state in `carry`, write no output    */
+  int32_t carry_tile0;    /* the state may cover more query rows than this call:   */
+  int32_t carry_tiles;    /* it then holds carry_tiles 128-row tiles per (batch,   */
+                          /* head) and this call's first row is tile carry_tile0   */
+                          /* of them (Nq of the earlier rows a multiple of 128).   */
+                          /* carry_tiles = 0: the state covers exactly this q.     */
 } MiniAttnFwdParams;
 
 /* Launch the forward kernel on `stream` (a cudaStream_t; NULL = default stream). */

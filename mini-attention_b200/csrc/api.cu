@@ -207,6 +207,11 @@ static int check_fwd_params(const MiniAttnFwdParams* p) {
       return fail(MINIATTN_EINVAL, "carry must be 256-byte aligned");
     if (p->kernel == MINIATTN_KERNEL_SIMPLE)
       return fail(MINIATTN_EUNSUPPORTED, "the carried state needs the warp-specialised kernel");
+    const int tiles = (p->Nq + ma::kTileM - 1) / ma::kTileM;
+    if (p->carry_tile0 < 0 || p->carry_tiles < 0 ||
+        (p->carry_tiles == 0 ? p->carry_tile0 != 0 : p->carry_tile0 + tiles > p->carry_tiles))
+      return fail(MINIATTN_EINVAL, "carry_tile0 (%d) + the %d Q tiles of this call exceed carry_tiles (%d)",
+                  p->carry_tile0, tiles, p->carry_tiles);
   }
   int rc;
   if ((rc = check_tensor(p->q, p->q_stride, p->D, "q")) != 0) return rc;
@@ -272,6 +277,8 @@ static void fill_args(const MiniAttnFwdParams* p, ma::FwdArgs* a) {
   a->carry_o = nullptr;
   a->carry_ml = nullptr;
   a->carry_mode = 0;
+  a->carry_tile0 = 0;
+  a->carry_tiles = 0;
 }
 
 static int check_device(int* sms) {
@@ -381,7 +388,9 @@ static int fwd_common(const MiniAttnFwdParams* p, void* scratch, size_t scratch_
   const int kd = kernel_head_dim(p->D);
   const bool carry = p->carry_in || p->carry_out;
   if (carry) {
-    const size_t rows = static_cast<size_t>(p->B) * p->Hq * a.n_q_tiles * ma::kTileM;
+    a.carry_tiles = p->carry_tiles > 0 ? p->carry_tiles : a.n_q_tiles;
+    a.carry_tile0 = p->carry_tile0;
+    const size_t rows = static_cast<size_t>(p->B) * p->Hq * a.carry_tiles * ma::kTileM;
     a.carry_o = static_cast<float*>(p->carry);
     a.carry_ml = reinterpret_cast<float2*>(static_cast<uint8_t*>(p->carry) + rows * kd * sizeof(float));
     a.carry_mode = (p->carry_in ? 1 : 0) | (p->carry_out ? 2 : 0);

@@ -29,9 +29,11 @@ struct FwdArgs {
   float2* part_ml;     // [slot][2 tiles][128 rows]: (row maximum in log2 units, row sum)
   int*    counters;    // [cut item][2 tiles][arrived, published]
   // Ring steps only (carry_mode != 0): the rows' running state between launches.
-  float*  carry_o;     // [B*Hq*n_q_tiles][D/4][128 rows][4] fp32, un-normalised O
-  float2* carry_ml;    // [B*Hq*n_q_tiles][128 rows]: (row maximum in log2 units, row sum)
+  float*  carry_o;     // [B*Hq*carry_tiles][D/4][128 rows][4] fp32, un-normalised O
+  float2* carry_ml;    // [B*Hq*carry_tiles][128 rows]: (row maximum in log2 units, row sum)
   int     carry_mode;  // bit 0: fold the stored state in; bit 1: store the new state, no output
+  int     carry_tile0; // the state holds carry_tiles tiles per (batch, head); this launch's first
+  int     carry_tiles; // Q tile is number carry_tile0 of them
 };
 
 // One CTA of a balanced launch, read from the launch's table (kernel parameter space).

@@ -517,7 +517,7 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if constexpr (CARRY) {
         if (a.carry_mode != 0) {
           const long long tix =
-              (static_cast<long long>(b) * a.Hq + h) * a.n_q_tiles + (q0 / kTileM + t);
+              (static_cast<long long>(b) * a.Hq + h) * a.carry_tiles + a.carry_tile0 + (q0 / kTileM + t);
           float* c_o = a.carry_o + tix * kTileM * D;
           float2* c_ml = a.carry_ml + tix * kTileM;
           constexpr uint32_t kPartBytes = D * kTileM * 4;

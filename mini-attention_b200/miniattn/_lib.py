@@ -30,6 +30,7 @@ class FwdParams(C.Structure):
         ("dtype", C.c_int32), ("causal", C.c_int32),
         ("softmax_scale", C.c_float), ("kernel", C.c_int32),
         ("carry", C.c_void_p), ("carry_in", C.c_int32), ("carry_out", C.c_int32),
+        ("carry_tile0", C.c_int32), ("carry_tiles", C.c_int32),
     ]
 
 

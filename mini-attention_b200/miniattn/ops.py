@@ -178,6 +178,7 @@ def flash_attn_fwd(
     carry: Optional[torch.Tensor] = None,
     carry_in: bool = False,
     carry_out: bool = False,
+    carry_rows: Optional[Tuple[int, int]] = None,
 ):
     """O = softmax(Q K^T * scale [+ causal mask]) V on the GPU.
 
@@ -196,6 +197,8 @@ def flash_attn_fwd(
     blocks, as the ring launcher does: with ``carry_out`` the rows' running (maximum, sum,
     un-normalised O) are stored in it and nothing is returned; with ``carry_in`` the stored state is
     folded into this call's result.  The last call of a chain (``carry_in`` only) returns the output.
+    ``carry_rows=(first_row, total_rows)``: the buffer was made for a longer q of `total_rows` rows and
+    this call's q is the row range of it that starts at `first_row` (a multiple of 128).
 
     The launch is asynchronous.  Every device-side wait is bounded; one that runs out sets a bit in a
     per-device status word instead of hanging — poll it with :func:`check_device_status` /
@@ -210,7 +213,7 @@ def flash_attn_fwd(
         key = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr() if out is not None else 0,
                q.shape, q.stride(), k.shape, k.stride(), v.stride(), out.stride() if out is not None else None,
                q.dtype, q.device.index, causal, softmax_scale, layout, return_lse, kernel, q_pos0, k_pos0, balance,
-               carry.data_ptr() if carry is not None else 0, carry_in, carry_out)
+               carry.data_ptr() if carry is not None else 0, carry_in, carry_out, carry_rows)
         hit = _param_cache.get(key)
     except (AttributeError, TypeError):   # not tensors: let the validation below say so
         key, hit = None, None
@@ -230,7 +233,16 @@ def flash_attn_fwd(
         p, out, lse = _prepare(q, k, v, causal, softmax_scale, layout, return_lse, out, kernel, q_pos0, k_pos0,
                                need_out=not carry_out)
         if p is not None and use_carry:
-            need_c = _lib.lib.miniattn_fwd_carry_bytes(C.byref(p))
+            if carry_rows is not None:
+                first, total = carry_rows
+                if first % 128 != 0 or first < 0 or first + p.Nq > total:
+                    raise RuntimeError("carry_rows: the first row must be a multiple of 128 inside the state's rows")
+                p.carry_tile0, p.carry_tiles = first // 128, (total + 127) // 128
+                whole = _lib.FwdParams()
+                whole.B, whole.Hq, whole.Hkv, whole.Nq, whole.Nk, whole.D = p.B, p.Hq, p.Hkv, total, p.Nk, p.D
+                need_c = _lib.lib.miniattn_fwd_carry_bytes(C.byref(whole))
+            else:
+                need_c = _lib.lib.miniattn_fwd_carry_bytes(C.byref(p))
             if need_c < 0:
                 _lib.check(int(need_c), "miniattn_fwd_carry_bytes")
             if not carry.is_cuda or carry.device != q.device or carry.numel() * carry.element_size() < need_c:

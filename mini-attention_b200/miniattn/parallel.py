@@ -156,6 +156,7 @@ def ring_forward(
     exchange: Optional[Callable] = None,
     verify_origin: bool = False,
     fused: bool = True,
+    merge_steps: bool = True,
 ) -> torch.Tensor:
     """Ring / context-parallel attention of this rank's zig-zag shard.
 
@@ -184,7 +185,16 @@ def ring_forward(
     out = torch.empty_like(q_local)
     if fused:
         from .ops import carry_state, flash_attn_fwd
-        states = [carry_state(q_blocks[0]), carry_state(q_blocks[1])]
+        # one state buffer for all 2L local rows; a launch on one block addresses its half of it
+        # (needs the late block to start on a tile boundary, else one buffer per block)
+        joint = L % 128 == 0
+        if joint:
+            state_all = carry_state(q_local)
+            states = [state_all, state_all]
+            rows_of = [(0, L2), (L, L2)]
+        else:
+            states = [carry_state(q_blocks[0]), carry_state(q_blocks[1])]
+            rows_of = [None, None]
         started = [False, False]
     else:
         accs = [accumulator(q_blocks[0]), accumulator(q_blocks[1])]
@@ -199,7 +209,28 @@ def ring_forward(
         if s + 1 < world:
             nk, nv = bufs[s % 2]
             handle = exchange(k_cur, v_cur, nk, nv)
-        for t in ring_step_tasks(rank, world, s, causal):
+        tasks = ring_step_tasks(rank, world, s, causal)
+        if fused and joint and merge_steps and _merge_step(tasks, remaining, started):
+            # The step's block pairs are all unmasked and share their Q block or their K/V block (or,
+            # without a mask, cover everything): one launch over the contiguous union, half the
+            # state round trips and twice the work per CTA.
+            qh = sorted({t.q_half for t in tasks})
+            kh = sorted({t.kv_half for t in tasks})
+            q_sel = q_local if len(qh) == 2 else q_blocks[qh[0]]
+            k_sel = k_cur if len(kh) == 2 else k_cur[:, :, kh[0] * L:(kh[0] + 1) * L]
+            v_sel = v_cur if len(kh) == 2 else v_cur[:, :, kh[0] * L:(kh[0] + 1) * L]
+            for t in tasks:
+                remaining[t.q_half] -= 1
+            last = all(remaining[h_] == 0 for h_ in qh)
+            out_sel = out if len(qh) == 2 else outs[qh[0]]
+            flash_attn_fwd(q_sel, k_sel, v_sel, causal=False, softmax_scale=softmax_scale,
+                           out=out_sel if last else None, carry=state_all,
+                           carry_in=all(started[h_] for h_ in qh), carry_out=not last,
+                           carry_rows=(0, L2) if len(qh) == 2 else rows_of[qh[0]])
+            for h_ in qh:
+                started[h_] = True
+            tasks = []
+        for t in tasks:
             kb = k_cur[:, :, t.kv_half * L:(t.kv_half + 1) * L]
             vb = v_cur[:, :, t.kv_half * L:(t.kv_half + 1) * L]
             remaining[t.q_half] -= 1
@@ -210,7 +241,7 @@ def ring_forward(
                 flash_attn_fwd(q_blocks[t.q_half], kb, vb, causal=t.causal, q_pos0=t.q_block * L,
                                k_pos0=t.kv_block * L, softmax_scale=softmax_scale,
                                out=outs[t.q_half] if last else None, carry=states[t.q_half],
-                               carry_in=started[t.q_half], carry_out=not last)
+                               carry_in=started[t.q_half], carry_out=not last, carry_rows=rows_of[t.q_half])
                 started[t.q_half] = True
                 continue
             o, lse = attn_fn(q_blocks[t.q_half], kb, vb, t.causal, t.q_block * L, t.kv_block * L, softmax_scale)
@@ -225,6 +256,22 @@ def ring_forward(
                     raise RuntimeError(f"ring step {s + 1} on rank {rank}: received the K/V pair of rank {got}, "
                                        f"expected rank {want}")
     return out
+
+
+def _merge_step(tasks: Sequence[RingTask], remaining: Sequence[int], started: Sequence[bool]) -> bool:
+    """Can the tasks of one ring step run as a single launch?  They must be unmasked and form a
+    full rectangle of (Q blocks) x (K/V blocks); the Q blocks must agree on whether a state exists
+    yet and on whether this step is their last."""
+    if len(tasks) < 2 or any(t.causal for t in tasks):
+        return False
+    qh = sorted({t.q_half for t in tasks})
+    kh = sorted({t.kv_half for t in tasks})
+    if len(tasks) != len(qh) * len(kh):
+        return False
+    per_q = len(kh)
+    if len({started[h] for h in qh}) != 1:
+        return False
+    return len({remaining[h] == per_q for h in qh}) == 1
 
 
 def ring_process_group(ranks: Optional[Sequence[int]] = None):

@@ -81,6 +81,8 @@ def _params(**kw):
         (dict(carry_out=1, carry=0x1010), -1, "256-byte aligned"),
         (dict(carry_out=1, carry=0x1000, kernel=1), -2, "warp-specialised"),
         (dict(carry_in=3, carry=0x1000), -1, "0 or 1"),
+        (dict(carry_out=1, carry=0x1000, carry_tile0=1), -1, "exceed carry_tiles"),
+        (dict(carry_out=1, carry=0x1000, carry_tile0=2, carry_tiles=2), -1, "exceed carry_tiles"),
         (dict(Nq=-1), -1, "negative"),
         (dict(Hkv=3), -1, "multiple of Hkv"),
         (dict(causal=2), -1, "causal"),

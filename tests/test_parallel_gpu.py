@@ -133,3 +133,15 @@ def test_shard_mode_rank_by_rank():
         par.sharded_forward(qd, kd, vd, causal=True, rank=r, world=4, out=out)
     ref = attention_reference(q, k, v, causal=True, out_dtype=torch.float32)
     assert (out.float().cpu() - ref).abs().max().item() <= TOL[torch.bfloat16]
+
+
+@pytest.mark.parametrize("N,world", [(1600, 2), (3072, 4), (2560, 2)])
+def test_ring_emulated_block_lengths(N, world):
+    """Block lengths that are and are not multiples of the 128-row tile: with whole tiles the two
+    resident blocks share one state buffer and a step's block pairs merge into one launch; without,
+    every block keeps its own state and every pair its own launch.  Same result either way."""
+    q, k, v = make_inputs(1, 2, 1, N, N, 128, torch.float16, seed=N)
+    out = par.ring_forward_emulated(q.to(DEV), k.to(DEV), v.to(DEV), world, causal=True).cpu()
+    ref = attention_reference(q, k, v, causal=True, out_dtype=torch.float32)
+    assert miniattn.device_status(DEV) == 0
+    assert (out.float() - ref).abs().max().item() <= TOL[torch.float16]

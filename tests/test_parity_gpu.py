@@ -403,3 +403,24 @@ def test_carried_state_rows_without_keys():
                                           causal=True, k_pos0=256 * blk, carry=state, carry_in=i > 0, carry_out=i < 1)
         assert maxerr(out.cpu(), ref) <= TOL[torch.float16]
     assert miniattn.device_status(DEV) == 0
+
+
+def test_carried_state_on_a_row_range():
+    """A state buffer made for 512 query rows serves calls on rows [0,256), [256,512) and on all of
+    them (carry_rows): what the ring launcher does with its two resident blocks."""
+    q, k, v = make_inputs(1, 2, 2, 512, 768, 128, torch.float16, seed=41)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ref = attention_reference(q, k, v, out_dtype=torch.float32)
+    state = miniattn.carry_state(qd)
+    lo, hi = qd[:, :, :256], qd[:, :, 256:]
+    k0, v0, k1, v1, k2, v2 = kd[:, :, :256], vd[:, :, :256], kd[:, :, 256:512], vd[:, :, 256:512], kd[:, :, 512:], vd[:, :, 512:]
+    miniattn.flash_attn_fwd(lo, k0, v0, carry=state, carry_out=True, carry_rows=(0, 512))
+    miniattn.flash_attn_fwd(hi, k0, v0, carry=state, carry_out=True, carry_rows=(256, 512))
+    miniattn.flash_attn_fwd(qd, k1, v1, carry=state, carry_in=True, carry_out=True, carry_rows=(0, 512))  # both halves at once
+    out = torch.empty_like(qd)
+    miniattn.flash_attn_fwd(lo, k2, v2, carry=state, carry_in=True, out=out[:, :, :256], carry_rows=(0, 512))
+    miniattn.flash_attn_fwd(hi, k2, v2, carry=state, carry_in=True, out=out[:, :, 256:], carry_rows=(256, 512))
+    assert miniattn.device_status(DEV) == 0
+    assert maxerr(out.cpu(), ref) <= TOL[torch.float16]
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        miniattn.flash_attn_fwd(qd[:, :, 100:356], k0, v0, carry=state, carry_out=True, carry_rows=(100, 512))
