@@ -179,7 +179,7 @@ __device__ __forceinline__ void quant_body(const uint16_t* __restrict__ x, long 
 }
 
 // Stage 1, one launch: the Q quantiser (nothing depends on it but the attention kernel) and the
-// partial column sums of K.  Blocks [0, q_blocks) quantise Q, the rest sum K.
+// partial column sums of K.  The first gridDim.x - q_blocks blocks sum K, the rest quantise Q.
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256)
 prepass_stage1_kernel(const uint16_t* __restrict__ q, long long qsb, long long qsh, long long qsn, int Nq,
@@ -188,12 +188,14 @@ prepass_stage1_kernel(const uint16_t* __restrict__ q, long long qsb, long long q
                       int Hkv, int nch, float* __restrict__ partial, int q_blocks) {
   // the dependent launch (stage 2) may start as soon as every CTA of this grid is under way
   cudaTriggerProgrammaticLaunchCompletion();
-  const int id = blockIdx.x;
-  if (id < q_blocks) {
+  // the column-sum CTAs read eight times as much as a quantiser CTA: they go first
+  const int s_blocks = static_cast<int>(gridDim.x) - q_blocks;
+  if (static_cast<int>(blockIdx.x) >= s_blocks) {
+    const int id = blockIdx.x - s_blocks;
     const int blk = id % nqb, h = (id / nqb) % Hq, b = id / (nqb * Hq);
     quant_body<D, BF16, false>(q, qsb, qsh, qsn, Nq, nullptr, 0, q8, sq, fold, nullptr, blk, h, b, Hq, nqb);
   } else {
-    const int c = id - q_blocks;
+    const int c = blockIdx.x;
     const int chunk = c % nch, h = (c / nch) % Hkv, b = c / (nch * Hkv);
     colsum_body<D, BF16>(k, ksb, ksh, ksn, Nk, partial, nch, chunk, h, b, Hkv);
   }

@@ -424,3 +424,42 @@ def test_carried_state_on_a_row_range():
     assert maxerr(out.cpu(), ref) <= TOL[torch.float16]
     with pytest.raises(RuntimeError, match="multiple of 128"):
         miniattn.flash_attn_fwd(qd[:, :, 100:356], k0, v0, carry=state, carry_out=True, carry_rows=(100, 512))
+
+
+def test_repeated_calls_reuse_the_parameter_block_safely():
+    """The operator caches the parameter block of a call by pointers, shapes, strides and flags.
+    Calls that hit the cache must still return fresh outputs, honour changed flags, and see new
+    values written into the same input tensors."""
+    q, k, v = make_inputs(1, 2, 2, 256, 256, 128, torch.float16, seed=61)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ref = attention_reference(q, k, v, out_dtype=torch.float32)
+    ref_c = attention_reference(q, k, v, causal=True, out_dtype=torch.float32)
+    a = miniattn.flash_attn_fwd(qd, kd, vd)
+    b = miniattn.flash_attn_fwd(qd, kd, vd)                       # cache hit, no `out` given
+    assert a.data_ptr() != b.data_ptr() and torch.equal(a, b)
+    c = miniattn.flash_attn_fwd(qd, kd, vd, causal=True)          # same tensors, other flag
+    o2, lse2 = miniattn.flash_attn_fwd(qd, kd, vd, return_lse=True)
+    o3, lse3 = miniattn.flash_attn_fwd(qd, kd, vd, return_lse=True)   # fresh lse per call
+    assert lse2.data_ptr() != lse3.data_ptr() and torch.equal(lse2, lse3)
+    assert maxerr(a.cpu(), ref) <= TOL[torch.float16] and maxerr(c.cpu(), ref_c) <= TOL[torch.float16]
+    assert maxerr(o3.cpu(), ref) <= TOL[torch.float16]
+    # new values in the same storage
+    q2, _, _ = make_inputs(1, 2, 2, 256, 256, 128, torch.float16, seed=62)
+    qd.copy_(q2)
+    d = miniattn.flash_attn_fwd(qd, kd, vd)
+    assert maxerr(d.cpu(), attention_reference(q2, k, v, out_dtype=torch.float32)) <= TOL[torch.float16]
+    # a caller-provided output is written in place, every time
+    out = torch.zeros_like(qd)
+    for _ in range(2):
+        out.zero_()
+        assert miniattn.flash_attn_fwd(qd, kd, vd, out=out) is out
+        assert maxerr(out, d) == 0
+    # a view with the same base pointer but other strides is another problem
+    wide = torch.randn(1, 4, 256, 128, dtype=torch.float16, device=DEV)
+    e = miniattn.flash_attn_fwd(wide[:, :2], kd, vd)
+    f = miniattn.flash_attn_fwd(wide[:, ::2], kd, vd)
+    assert maxerr(e.cpu(), attention_reference(wide[:, :2].cpu(), k, v, out_dtype=torch.float32)) <= TOL[torch.float16]
+    assert maxerr(f.cpu(), attention_reference(wide[:, ::2].cpu(), k, v, out_dtype=torch.float32)) <= TOL[torch.float16]
+    with pytest.raises(RuntimeError, match="same data type"):
+        miniattn.flash_attn_fwd(qd, kd.bfloat16(), vd)
+    miniattn.check_device_status(DEV)   # raises if any bounded wait ran out
