@@ -393,7 +393,10 @@ fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       // A CTA that covers a piece of an item's key range publishes its partial result; the last
       // piece to arrive folds the other pieces into its own accumulator and writes the output.
-      float f_self = (l_run > 0.f) ? (1.f / l_run) : 0.f;  // factor of this CTA's own accumulator
+      // factor of this CTA's own accumulator; a row that never saw a visible key (running maximum
+      // still -inf) yields zeros even though its masked scores left 2^-126 terms in l_run (the
+      // polynomial exp2 clamps its argument)
+      float f_self = (l_run > 0.f && m_cur != -INFINITY) ? (1.f / l_run) : 0.f;
       float f_part = 0.f;            // factor of the partial waiting in shared memory (if any)
       const float4* s_part = nullptr; // that partial: [D/4][128 rows][4] fp32, offset to this row
       bool write_out = true;

@@ -79,16 +79,20 @@ def test_softmax_scale_and_layouts(kernel):
     assert maxerr(out2, ref2) <= TOL[torch.float16]
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("kernel", KERNELS)
-def test_causal_offsets(kernel):
+def test_causal_offsets(kernel, dtype):
     """Global positions shift the diagonal (what a ring step needs); rows that see no key give
-    zeros and lse = -inf."""
-    q, k, v = make_inputs(1, 2, 2, 256, 384, 128, torch.float16, seed=5)
+    exact zeros and lse = -inf (in bf16 a masked score's 2^-126 does not round to zero: the rows
+    must come out zero all the same)."""
+    q, k, v = make_inputs(1, 2, 2, 256, 384, 128, dtype, seed=5)
     for q_pos0, k_pos0 in ((128, 0), (0, 128), (300, 100), (0, 400)):
         ref, ref_lse = attention_reference(q, k, v, causal=True, q_pos0=q_pos0, k_pos0=k_pos0,
                                            return_lse=True, out_dtype=torch.float32)
         out, lse = run(q, k, v, causal=True, q_pos0=q_pos0, k_pos0=k_pos0, kernel=kernel, return_lse=True)
-        assert maxerr(out, ref) <= TOL[torch.float16], (q_pos0, k_pos0)
+        assert maxerr(out, ref) <= TOL[dtype], (q_pos0, k_pos0)
+        dark = ~torch.isfinite(ref_lse)
+        assert float(out[dark].abs().max() if dark.any() else 0.0) == 0.0
         finite = torch.isfinite(ref_lse)
         assert torch.equal(torch.isfinite(lse), finite)
         if finite.any():
