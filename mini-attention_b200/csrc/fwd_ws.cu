@@ -28,6 +28,14 @@
 // The row maximum is updated lazily: a row keeps exponentiating against a stale maximum until the
 // true maximum has grown by more than 2^8 (in the exp2 domain), so the O accumulator is rescaled
 // only rarely; l is accumulated against the same maximum, which keeps O / l exact.
+//
+// Softmax arithmetic runs two scores per issue slot (packed f32x2 FMA / ADD); a share of the
+// exponentials is evaluated by a cubic on the FMA pipe instead of the exp2 unit.
+//
+// Template variants of the one kernel: QK8 (int8 Q K^T, accumulator pre-biased so that the scores
+// arrive as floats), PLAN (balanced launch: work items cut over several CTAs, merged by the last
+// to arrive), CARRY (ring steps: the rows' running state is read from and written to global
+// memory in the epilogue instead of a second, merging launch).
 #include <atomic>
 #include <type_traits>
 
