@@ -14,6 +14,9 @@ Each fixture stores seeded inputs and the output the reference function produced
 * ``gqa_core`` / ``mqa_core`` / ``mha_core``  the core attention call inside ``GQA_Flash``,
   ``MQA_Flash`` and ``MHA`` (kernels/standard/pytorch/{gqa,mqa,mha}.py) with the q, k, v the
   module fed into it, captured by wrapping the module's attention call.
+* ``mha_module``  the ``MHA`` module of kernels/standard/pytorch/mha.py run whole (d_model 128, 2 heads, 64
+  tokens): its parameters, its input and both return values without a mask and with a lower-triangular
+  mask, plus the fact that an all-ones mask changes nothing.
 
 Inputs are stored in fp16/bf16 bit patterns (uint16 views) so that loading is exact.
 """
