@@ -210,40 +210,28 @@ def ring_forward(
             nk, nv = bufs[s % 2]
             handle = exchange(k_cur, v_cur, nk, nv)
         tasks = ring_step_tasks(rank, world, s, causal)
-        if fused and joint and merge_steps and _merge_step(tasks, remaining, started):
-            # The step's block pairs are all unmasked and share their Q block or their K/V block (or,
-            # without a mask, cover everything): one launch over the contiguous union, half the
-            # state round trips and twice the work per CTA.
-            qh = sorted({t.q_half for t in tasks})
-            kh = sorted({t.kv_half for t in tasks})
-            q_sel = q_local if len(qh) == 2 else q_blocks[qh[0]]
-            k_sel = k_cur if len(kh) == 2 else k_cur[:, :, kh[0] * L:(kh[0] + 1) * L]
-            v_sel = v_cur if len(kh) == 2 else v_cur[:, :, kh[0] * L:(kh[0] + 1) * L]
-            for t in tasks:
-                remaining[t.q_half] -= 1
-            last = all(remaining[h_] == 0 for h_ in qh)
-            out_sel = out if len(qh) == 2 else outs[qh[0]]
-            flash_attn_fwd(q_sel, k_sel, v_sel, causal=False, softmax_scale=softmax_scale,
-                           out=out_sel if last else None, carry=state_all,
-                           carry_in=all(started[h_] for h_ in qh), carry_out=not last,
-                           carry_rows=(0, L2) if len(qh) == 2 else rows_of[qh[0]])
-            for h_ in qh:
-                started[h_] = True
+        if fused:
+            # one launch per entry: state in (after a block's first task), state out or, on a block's
+            # last task, the finished rows straight into the output
+            for ln in ring_step_launches(tasks, remaining, started, joint and merge_steps):
+                qh, kh = ln.q_halves, ln.kv_halves
+                q_sel = q_local if len(qh) == 2 else q_blocks[qh[0]]
+                k_sel = k_cur if len(kh) == 2 else k_cur[:, :, kh[0] * L:(kh[0] + 1) * L]
+                v_sel = v_cur if len(kh) == 2 else v_cur[:, :, kh[0] * L:(kh[0] + 1) * L]
+                out_sel = out if len(qh) == 2 else outs[qh[0]]
+                if len(qh) == 2:
+                    state, rows = state_all, (0, L2)
+                else:
+                    state, rows = states[qh[0]], rows_of[qh[0]]
+                flash_attn_fwd(q_sel, k_sel, v_sel, causal=ln.causal, q_pos0=ln.q_block * L, k_pos0=ln.kv_block * L,
+                               softmax_scale=softmax_scale, out=out_sel if ln.last else None, carry=state,
+                               carry_in=ln.carry_in, carry_out=not ln.last, carry_rows=rows)
             tasks = []
         for t in tasks:
             kb = k_cur[:, :, t.kv_half * L:(t.kv_half + 1) * L]
             vb = v_cur[:, :, t.kv_half * L:(t.kv_half + 1) * L]
             remaining[t.q_half] -= 1
             last = remaining[t.q_half] == 0
-            if fused:
-                # one launch: state in (after the block's first task), state out or, on the block's
-                # last task, the finished rows straight into the output
-                flash_attn_fwd(q_blocks[t.q_half], kb, vb, causal=t.causal, q_pos0=t.q_block * L,
-                               k_pos0=t.kv_block * L, softmax_scale=softmax_scale,
-                               out=outs[t.q_half] if last else None, carry=states[t.q_half],
-                               carry_in=started[t.q_half], carry_out=not last, carry_rows=rows_of[t.q_half])
-                started[t.q_half] = True
-                continue
             o, lse = attn_fn(q_blocks[t.q_half], kb, vb, t.causal, t.q_block * L, t.kv_block * L, softmax_scale)
             # the last merge of a block writes the finished rows straight into the output
             accs[t.q_half].add(o, lse, out=outs[t.q_half] if last else None)
@@ -255,6 +243,48 @@ def ring_forward(
                 if got != want:
                     raise RuntimeError(f"ring step {s + 1} on rank {rank}: received the K/V pair of rank {got}, "
                                        f"expected rank {want}")
+    return out
+
+
+@dataclass(frozen=True)
+class RingLaunch:
+    """One attention launch of a ring step in the carried-state form."""
+
+    q_halves: Tuple[int, ...]    # resident Q blocks covered (0 = early, 1 = late); both = all 2L rows
+    kv_halves: Tuple[int, ...]   # blocks of the visiting pair covered; both = all 2L keys
+    causal: bool                 # True only for a single diagonal block pair
+    q_block: int                 # global block indices of the first covered blocks (positions of a
+    kv_block: int                # causal launch; ignored by an unmasked one)
+    carry_in: bool               # the covered rows have a state from earlier launches
+    last: bool                   # no later launch touches the covered rows: write the output
+
+
+def ring_step_launches(tasks: Sequence[RingTask], remaining: List[int], started: List[bool],
+                       merge: bool) -> List[RingLaunch]:
+    """Launches of one ring step, and the bookkeeping that goes with them: `remaining[h]` (tasks
+    resident block h still has to receive) and `started[h]` (block h has a state) are updated.
+    With `merge` a step whose block pairs are all unmasked and form a full rectangle of
+    (Q blocks) x (K/V blocks) — they share their Q block or their K/V block, or, without a mask,
+    cover everything — becomes one launch over the contiguous union: half the state round trips
+    where the Q block is shared, twice the work per CTA."""
+    out: List[RingLaunch] = []
+    if merge and _merge_step(tasks, remaining, started):
+        qh = tuple(sorted({t.q_half for t in tasks}))
+        kh = tuple(sorted({t.kv_half for t in tasks}))
+        carry_in = all(started[h] for h in qh)
+        for t in tasks:
+            remaining[t.q_half] -= 1
+        last = all(remaining[h] == 0 for h in qh)
+        first = min(tasks, key=lambda t: (t.q_half, t.kv_half))
+        out.append(RingLaunch(qh, kh, False, first.q_block, first.kv_block, carry_in, last))
+        for h in qh:
+            started[h] = True
+        return out
+    for t in tasks:
+        remaining[t.q_half] -= 1
+        out.append(RingLaunch((t.q_half,), (t.kv_half,), t.causal, t.q_block, t.kv_block, started[t.q_half],
+                              remaining[t.q_half] == 0))
+        started[t.q_half] = True
     return out
 
 

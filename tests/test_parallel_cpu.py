@@ -170,3 +170,47 @@ def test_ring_detects_a_repeated_hop():
     the origin check must refuse it instead of silently merging the same keys twice."""
     for rank, status, msg in _run_ring(2, True, fault="repeat"):
         assert status == "error" and "expected rank" in msg
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("merge", [True, False])
+def test_ring_launch_plan_covers_every_block_pair_once(world, causal, merge):
+    """The carried-state launch plan of every rank: each (Q block, K/V block) pair of the schedule is
+    covered by exactly one launch; a block's first launch has no state to read, all later ones do;
+    exactly the last launch of a block writes its output; merged launches are unmasked rectangles."""
+    n_launches = {True: 0, False: 0}
+    for rank in range(world):
+        remaining, started = [0, 0], [False, False]
+        for s in range(world):
+            for t in par.ring_step_tasks(rank, world, s, causal):
+                remaining[t.q_half] += 1
+        covered = []
+        finished = [False, False]
+        for s in range(world):
+            tasks = par.ring_step_tasks(rank, world, s, causal)
+            was_started = list(started)
+            launches = par.ring_step_launches(tasks, remaining, started, merge)
+            n_launches[merge] += len(launches)
+            seen_in_step = [False, False]
+            for ln in launches:
+                if len(ln.q_halves) * len(ln.kv_halves) > 1:
+                    assert merge and not ln.causal
+                for qh in ln.q_halves:
+                    assert not finished[qh], "a block was written out and then touched again"
+                    assert ln.carry_in == (was_started[qh] or seen_in_step[qh])
+                    for kh in ln.kv_halves:
+                        covered.append((qh, s, kh))
+                for qh in ln.q_halves:
+                    seen_in_step[qh] = True
+                    if ln.last:
+                        finished[qh] = True
+            want_step = sorted((t.q_half, s, t.kv_half) for t in tasks)
+            assert sorted(c for c in covered if c[1] == s) == want_step
+        assert remaining == [0, 0] and finished == [True, True]
+    if merge and world > 1:
+        # per rank: three launches in the first step, then one per step, plus one where the early
+        # block ends before the late one (against 2 * world + 1 without merging)
+        assert n_launches[True] <= (world + 3) * world
+        if causal and world >= 4:
+            assert n_launches[True] < (2 * world + 1) * world
